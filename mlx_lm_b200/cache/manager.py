@@ -128,7 +128,8 @@ class CacheManager:
         self.kv_groups: List[KVGroup] = []
         self.state_groups: List[StateGroup] = []
         self._where: Dict[int, Tuple[str, int]] = {}   # cache id -> ("kv" | "state", group index)
-        for cid in sorted(cache_specs):
+        # a key is a cache number, or (number, name) for one of several caches of a block
+        for cid in sorted(cache_specs, key=lambda k: (k[0], str(k[1])) if isinstance(k, tuple) else (k, "")):
             spec = cache_specs[cid]
             if isinstance(spec, PagedKVSpec):
                 for gi, g in enumerate(self.kv_groups):
@@ -178,8 +179,12 @@ class CacheManager:
                 n += g.data.numel() * 4
         return n
 
-    def where(self, cache_id: int) -> Tuple[str, int]:
+    def where(self, cache_id) -> Tuple[str, int]:
         return self._where[cache_id]
+
+    def names_of(self, number: int) -> List[str]:
+        """The names under which cache ``number`` holds several caches (``(number, name)`` keys); empty if it is one."""
+        return [k[1] for k in self._where if isinstance(k, tuple) and k[0] == number]
 
     # ------------------------------------------------------------ requests
     def add_request(self, rid: Hashable) -> int:

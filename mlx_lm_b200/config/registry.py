@@ -43,10 +43,14 @@ def get_architecture(config: dict) -> Architecture:
     one, worded as mlx-lm words it (mlx_lm/utils.py:189-193)."""
     import mlx_lm_b200.models  # noqa: F401  (registers the built-in architectures)
 
-    if "model_type" not in config:
+    # the architecture's name: ``model_type``, or ``architecture`` (a string) where a config has no ``model_type``
+    name = config.get("model_type")
+    if name is None and isinstance(config.get("architecture"), str):
+        name = config["architecture"]
+    if name is None:
         raise ConfigError("config.json lacks required key(s): model_type")
-    model_type = MODEL_REMAPPING.get(config["model_type"], config["model_type"])
-    arch = _ARCHITECTURES.get(model_type)
+    model_type = MODEL_REMAPPING.get(name, name)
+    arch = _ARCHITECTURES.get(model_type) or _ARCHITECTURES.get(str(model_type).lower())
     if arch is None:
         raise ConfigError(f"Model type {model_type} not supported. Known: {sorted(_ARCHITECTURES)}")
     return arch

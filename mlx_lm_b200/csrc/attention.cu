@@ -96,7 +96,7 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, const int* __restrict
                          int max_pages, int n_pages, int page, int Hq, int Hkv, int Dh, int window,
                          float scale, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                          T* __restrict__ out, int ldo, const int* __restrict__ rows, int n_tokens,
-                         int* __restrict__ status) {
+                         int* __restrict__ status, const float* __restrict__ sinks) {
   extern __shared__ float sq[];  // [warps][Dh]
   pdl_trigger();
   pdl_wait();
@@ -160,6 +160,7 @@ attention_generic_kernel(const T* __restrict__ q, int ldq, const int* __restrict
       }
     }
   }
+  if (sinks && m != -INFINITY) l += expf(sinks[h] - m);   // the sink: a term of the denominator without a value
   const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
   for (int i = 0; i < MAX_DPL; ++i) {
@@ -201,7 +202,7 @@ MLXB_EXPORT int mlxb_attention_generic(int dtype, const void* q, int ldq, const 
                                        const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                                        int Dh, int window, float scale, const void* k_pool, const void* v_pool,
                                        void* out, int ldo, const int* rows, int n_tokens, int* status,
-                                       cudaStream_t stream) {
+                                       cudaStream_t stream, const float* sinks) {
   if (n_tokens <= 0) return 0;
   if (int e = check_common("attention", page, Hq, Hkv, Dh)) return e;
   const int warps = 4;
@@ -211,12 +212,12 @@ MLXB_EXPORT int mlxb_attention_generic(int dtype, const void* q, int ldq, const 
   if (dtype == MLXB_F32)
     launch_pdl(attention_generic_kernel<float>, dim3(blocks), dim3(warps * 32), smem, stream,
         (const float*)q, ldq, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window, scale,
-        (const float*)k_pool, (const float*)v_pool, (float*)out, ldo, rows, n_tokens, status);
+        (const float*)k_pool, (const float*)v_pool, (float*)out, ldo, rows, n_tokens, status, sinks);
   else if (dtype == MLXB_BF16)
     launch_pdl(attention_generic_kernel<__nv_bfloat16>, dim3(blocks), dim3(warps * 32), smem, stream,
         (const __nv_bfloat16*)q, ldq, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window,
         scale, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, ldo, rows, n_tokens,
-        status);
+        status, sinks);
   else
     return mlxb_fail(MLXB_BAD_DTYPE, "attention: dtype code %d", dtype);
   return mlxb_check_launch("attention (generic)");
@@ -293,7 +294,7 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
                         const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                         int Dh, int window, float scale, const T* __restrict__ k_pool, const T* __restrict__ v_pool,
                         float* partial, int* counters, int n_chunks_max, int chunk, T* __restrict__ out, int ldo,
-                        int* __restrict__ status) {
+                        int* __restrict__ status, const float* __restrict__ sinks) {
   constexpr int GROUPS = DEC_THREADS / TPK;
   constexpr int U = sizeof(T) == 2 ? 8 : 4;   // keys in flight per thread
   extern __shared__ float sm[];               // per warp: m | l | o[Dh]
@@ -473,6 +474,7 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
   }
 
   if (c0 == c1) {   // the only chunk of this row: no partial results, no ticket
+    if (sinks && M != -INFINITY) L += expf(sinks[h] - M);   // the sink counts once, with the row's last (here: only) chunk
     const float inv = L > 0.f ? 1.f / L : 0.f;
     for (int d = threadIdx.x; d < Dh; d += DEC_THREADS) {
       float acc = 0.f;
@@ -511,6 +513,7 @@ attention_decode_kernel(const T* __restrict__ q, int ldq, const int* __restrict_
   float Ls = 0.f;
   for (int cc = c0; cc <= c1; ++cc)
     Ls += __ldcg(src + (size_t)cc * (Dh + 2) + 1) * expf(__ldcg(src + (size_t)cc * (Dh + 2)) - Mx);
+  if (sinks && Mx != -INFINITY) Ls += expf(sinks[h] - Mx);
   const float inv = Ls > 0.f ? 1.f / Ls : 0.f;
   for (int d = threadIdx.x; d < Dh; d += DEC_THREADS) {
     float acc = 0.f;
@@ -526,7 +529,7 @@ static int launch_decode(const void* q, int ldq, const int* rows, const int* pos
                          const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv, int Dh,
                          int window, float scale, const void* k_pool, const void* v_pool, float* partial,
                          int* counters, int n_chunks_max, int chunk, void* out, int ldo, int n_rows, int* status,
-                         cudaStream_t stream) {
+                         cudaStream_t stream, const float* sinks) {
   const int chunks8 = (Dh + 7) / 8;
   int tpk = 2;
   while (tpk < chunks8) tpk <<= 1;
@@ -544,7 +547,8 @@ static int launch_decode(const void* q, int ldq, const int* rows, const int* pos
     const size_t smem = (size_t)(TH_ / 32) * (Dh + 2) * sizeof(float);                                               \
     launch_pdl(attention_decode_kernel<T, TPK_, TH_>, grid, dim3(TH_), smem, stream, (const T*)q, ldq, rows,         \
                positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv, Dh, window, scale,              \
-               (const T*)k_pool, (const T*)v_pool, partial, counters, n_chunks_max, chunk, (T*)out, ldo, status);    \
+               (const T*)k_pool, (const T*)v_pool, partial, counters, n_chunks_max, chunk, (T*)out, ldo, status,     \
+               sinks);                                                                                               \
   }
 #define DEC(TPK_) { if (many) DEC2(TPK_, 256) else DEC2(TPK_, 512) }
   if (tpk == 2) DEC(2) else if (tpk == 4) DEC(4) else if (tpk == 8) DEC(8) else if (tpk == 16) DEC(16) else DEC(32)
@@ -568,7 +572,8 @@ MLXB_EXPORT int mlxb_attention_decode(int dtype, const void* q, int ldq, const i
                                       const int* token_req, const int* block_table, int max_pages, int n_pages,
                                       int page, int Hq, int Hkv, int Dh, int window, float scale, const void* k_pool,
                                       const void* v_pool, float* partial, int* counters, int n_chunks_max, int chunk,
-                                      void* out, int ldo, int n_rows, int* status, cudaStream_t stream) {
+                                      void* out, int ldo, int n_rows, int* status, cudaStream_t stream,
+                                      const float* sinks) {
   if (n_rows <= 0) return 0;
   if (int e = check_common("attention (single-token rows)", page, Hq, Hkv, Dh)) return e;
   if (Dh % 8) return mlxb_fail(MLXB_BAD_ARG, "attention (single-token rows): head size %d is not a multiple of 8", Dh);
@@ -581,11 +586,11 @@ MLXB_EXPORT int mlxb_attention_decode(int dtype, const void* q, int ldq, const i
   if (dtype == MLXB_F32)
     return launch_decode<float>(q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page, Hq, Hkv,
                                 Dh, window, scale, k_pool, v_pool, partial, counters, n_chunks_max, chunk, out, ldo,
-                                n_rows, status, stream);
+                                n_rows, status, stream, sinks);
   if (dtype == MLXB_BF16)
     return launch_decode<__nv_bfloat16>(q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page, Hq,
                                         Hkv, Dh, window, scale, k_pool, v_pool, partial, counters, n_chunks_max, chunk,
-                                        out, ldo, n_rows, status, stream);
+                                        out, ldo, n_rows, status, stream, sinks);
   return mlxb_fail(MLXB_BAD_DTYPE, "attention (single-token rows): dtype code %d", dtype);
 }
 
@@ -643,5 +648,5 @@ MLXB_EXPORT int mlxb_attention_decode_noalloc(int dtype, const void* q, int ldq,
   return mlxb_attention_decode(dtype, q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page,
                                n_q_heads, n_kv_heads, head_dim, window, scale, k_pool, v_pool,
                                g_noalloc_partial_ptr[dev], g_noalloc_counters_ptr[dev], n_chunks_max, chunk, out, ldo,
-                               n_rows, status, stream);
+                               n_rows, status, stream, nullptr);
 }

@@ -85,7 +85,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
                          const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                          int window, float scale_log2e, const __nv_bfloat16* __restrict__ k_pool,
                          const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, int ldo,
-                         int* __restrict__ status) {
+                         int* __restrict__ status, const float* __restrict__ sinks) {
   constexpr int THREADS = QW * 32;            // threads of one group: they gather and use the same key blocks
   constexpr int STRIDE = DH + 8;              // elements per shared-memory row (16 bytes of padding)
   constexpr int KS = DH / 16;                 // k steps of Q K^T
@@ -330,6 +330,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
   l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1);
   l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+  if (sinks) {   // the sink: one more term of the denominator, in the exponent's units, without a value
+    const float sk = sinks[h] * 1.4426950408889634f;
+    if (m_lo != -INFINITY) l_lo += fast_exp2(sk - m_lo);
+    if (m_hi != -INFINITY) l_hi += fast_exp2(sk - m_hi);
+  }
   const float inv_lo = l_lo > 0.f ? 1.f / l_lo : 0.f, inv_hi = l_hi > 0.f ? 1.f / l_hi : 0.f;
   __nv_bfloat16* o_lo = out + (size_t)(row0 + r_lo) * ldo + h * DH + 2 * qd;
   __nv_bfloat16* o_hi = out + (size_t)(row0 + r_hi) * ldo + h * DH + 2 * qd;
@@ -343,7 +348,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
 template <int DH, int QW, int KSPLIT>
 static int launch(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table, int max_pages,
                   int n_pages, int page, int Hq, int Hkv, int window, float scale, const void* k_pool,
-                  const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream) {
+                  const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream, const float* sinks) {
   constexpr int WARPS = QW * KSPLIT;
   size_t smem = (size_t)KSPLIT * 2 * 2 * BKV * (DH + 8) * sizeof(__nv_bfloat16);
   const size_t merge = (size_t)(KSPLIT - 1) * (DH / 8 * 4 + 4) * QW * 32 * sizeof(float);
@@ -357,7 +362,7 @@ static int launch(const void* q, int ldq, const int* tiles, int n_tiles, const i
   launch_pdl(kern, dim3(n_tiles, Hq), dim3(WARPS * 32), smem, stream, (const __nv_bfloat16*)q, ldq,
              (const int4*)tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window,
              scale * 1.4426950408889634f, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-             (__nv_bfloat16*)out, ldo, status);
+             (__nv_bfloat16*)out, ldo, status, sinks);
   return mlxb_check_launch("attention (portions)");
 }
 
@@ -368,7 +373,7 @@ static int launch(const void* q, int ldq, const int* tiles, int n_tiles, const i
 MLXB_EXPORT int mlxb_attention_prefill(const void* q, int ldq, const int* tiles, int n_tiles, int tile_rows,
                                        const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                                        int Dh, int window, float scale, const void* k_pool, const void* v_pool,
-                                       void* out, int ldo, int* status, cudaStream_t stream) {
+                                       void* out, int ldo, int* status, cudaStream_t stream, const float* sinks) {
   if (n_tiles <= 0) return 0;
   if (page <= 0 || (page & (page - 1))) return mlxb_fail(MLXB_BAD_ARG, "attention (portions): page size %d", page);
   if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || Hq > 65535)
@@ -381,9 +386,9 @@ MLXB_EXPORT int mlxb_attention_prefill(const void* q, int ldq, const int* tiles,
   case D:                                                                                                             \
     if (tile_rows == 128)                                                                                             \
       return launch<D, 8, 1>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,   \
-                             k_pool, v_pool, out, ldo, status, stream);                                               \
+                             k_pool, v_pool, out, ldo, status, stream, sinks);                                        \
     return launch<D, 4, 2>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,     \
-                           k_pool, v_pool, out, ldo, status, stream)
+                           k_pool, v_pool, out, ldo, status, stream, sinks)
   switch (Dh) {
     GO(16); GO(32); GO(48); GO(64); GO(80); GO(96); GO(112); GO(128);
     default:
@@ -417,7 +422,7 @@ attention_rows_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int4* 
                       const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                       int window, float scale_log2e, const __nv_bfloat16* __restrict__ k_pool,
                       const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, int ldo,
-                      int* __restrict__ status) {
+                      int* __restrict__ status, const float* __restrict__ sinks) {
   constexpr int THREADS = RW * 32;
   constexpr int STRIDE = DH + 8;              // elements per shared-memory row (16 bytes of padding)
   constexpr int KS = DH / 16;                 // k steps of q K^T
@@ -591,6 +596,7 @@ attention_rows_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int4* 
   float L = 0.f;
 #pragma unroll
   for (int w = 0; w < RW; ++w) L = fmaf(xch[w * (2 + DH) + 1], fast_exp2(xch[w * (2 + DH)] - base), L);
+  if (sinks && M != -INFINITY) L += fast_exp2(sinks[h] * 1.4426950408889634f - M);
   const float inv = L > 0.f ? 1.f / L : 0.f;
   for (int d = threadIdx.x; d < DH; d += THREADS) {
     float acc = 0.f;
@@ -603,7 +609,7 @@ attention_rows_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int4* 
 template <int DH, int RW, int RS>
 static int launch_rows(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table, int max_pages,
                        int n_pages, int page, int Hq, int Hkv, int window, float scale, const void* k_pool,
-                       const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream) {
+                       const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream, const float* sinks) {
   const size_t smem = (size_t)RS * 2 * BKV * (DH + 8) * sizeof(__nv_bfloat16);    // (the merge needs far less)
   auto kern = attention_rows_kernel<DH, RW, RS>;
   static bool raised = false;
@@ -613,7 +619,7 @@ static int launch_rows(const void* q, int ldq, const int* tiles, int n_tiles, co
   }
   launch_pdl(kern, dim3(n_tiles, Hq), dim3(RW * 32), smem, stream, (const __nv_bfloat16*)q, ldq, (const int4*)tiles,
              block_table, max_pages, n_pages, page, Hq, Hkv, window, scale * 1.4426950408889634f,
-             (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, ldo, status);
+             (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (__nv_bfloat16*)out, ldo, status, sinks);
   return mlxb_check_launch("attention (single rows)");
 }
 
@@ -622,7 +628,7 @@ static int launch_rows(const void* q, int ldq, const int* tiles, int n_tiles, co
 MLXB_EXPORT int mlxb_attention_rows(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table,
                                     int max_pages, int n_pages, int page, int Hq, int Hkv, int Dh, int window,
                                     float scale, const void* k_pool, const void* v_pool, void* out, int ldo,
-                                    int* status, cudaStream_t stream) {
+                                    int* status, cudaStream_t stream, const float* sinks) {
   if (n_tiles <= 0) return 0;
   if (page <= 0 || (page & (page - 1))) return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): page size %d", page);
   if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || Hq > 65535)
@@ -632,7 +638,7 @@ MLXB_EXPORT int mlxb_attention_rows(const void* q, int ldq, const int* tiles, in
 #define GO(D)                                                                                                         \
   case D:                                                                                                             \
     return launch_rows<D, 4, (D <= 64 ? 3 : 2)>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq,    \
-                                                Hkv, window, scale, k_pool, v_pool, out, ldo, status, stream)
+                                                Hkv, window, scale, k_pool, v_pool, out, ldo, status, stream, sinks)
   switch (Dh) {
     GO(16); GO(32); GO(48); GO(64); GO(80); GO(96); GO(112); GO(128);
     default:

@@ -140,7 +140,8 @@ __global__ void __launch_bounds__(AT_THREADS, 2)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, const int4* __restrict__ tiles,
                             const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
-                            int window, float scale_log2e, __nv_bfloat16* out, int ldo, int* __restrict__ status) {
+                            int window, float scale_log2e, __nv_bfloat16* out, int ldo, int* __restrict__ status,
+                            const float* __restrict__ sinks) {
   extern __shared__ uint8_t smem_raw[];
   AtSmem& sm = *reinterpret_cast<AtSmem*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -360,6 +361,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       l += sm.row_max[half ^ 1][r];
     }
     if (ok && r < n_rows) {
+      if (sinks && m != -INFINITY) l += fast_exp2(sinks[h] * 1.4426950408889634f - m);   // the sink: no key, no value
       const float inv = l > 0.f ? 1.f / l : 0.f;
       __nv_bfloat16* dst = out + (size_t)(row0 + r) * ldo + h * HD + half * (HD / 2);
 #pragma unroll
@@ -406,7 +408,8 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, int cols
 MLXB_EXPORT int mlxb_attention_prefill_tc(const void* q, int ldq, int n_tokens, const int* tiles, int n_tiles,
                                           const int* block_table, int max_pages, int n_pages, int page, int Hq,
                                           int Hkv, int Dh, int window, float scale, const void* k_pool,
-                                          const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream) {
+                                          const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream,
+                                          const float* sinks) {
   if (n_tiles <= 0) return 0;
   if (Dh != HD) return mlxb_fail(MLXB_BAD_ARG, "attention (portions, tcgen05): head size %d, this kernel takes %d", Dh, HD);
   if (page < 8 || page > TK || (page & (page - 1)))
@@ -431,6 +434,6 @@ MLXB_EXPORT int mlxb_attention_prefill_tc(const void* q, int ldq, int n_tokens, 
   }
   launch_pdl(attention_prefill_tc_kernel, dim3(n_tiles, Hq), dim3(AT_THREADS), smem, stream, mq, mk, mv,
              (const int4*)tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window,
-             scale * 1.4426950408889634f, (__nv_bfloat16*)out, ldo, status);
+             scale * 1.4426950408889634f, (__nv_bfloat16*)out, ldo, status, sinks);
   return mlxb_check_launch("attention (portions, tcgen05)");
 }

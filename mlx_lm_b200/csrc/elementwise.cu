@@ -1,0 +1,108 @@
+// Small row-wise kernels between the products of a layer.
+//   gated_unit      out[t, j] = act(in[t, j]) * in[t, F + j]: the two halves of a fused [gate | up] projection
+//                   (act: silu = z * sigmoid(z)); float32 arithmetic, rounded once.
+//   scale_by_rows   out[t, j] = in[t, j] * table[index[t], first + j]: a per-token vector looked up in a table.
+//   join_rows       out[t] = [a[t] | b[t]] in the activation dtype from float32 rows (b may be null: a plain cast).
+#include "common.cuh"
+
+MLXB_DEFINE_LAST_ERROR()
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+
+template <typename T>
+__global__ void gated_unit_kernel(const T* in, int ldi, T* __restrict__ out, int ldo, int F, int n) {
+  pdl_trigger();
+  pdl_wait();
+  in = after_wait(in);
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * F) return;
+  const int t = (int)(idx / F), j = (int)(idx - (long long)t * F);
+  const T* row = in + (size_t)t * ldi;
+  out[(size_t)t * ldo + j] = from_f<T>(silu_f(to_f(row[j])) * to_f(row[F + j]));
+}
+
+MLXB_EXPORT int mlxb_gated_unit(int dtype, const void* in, int ldi, void* out, int ldo, int F, int n_rows,
+                                cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (F <= 0 || ldi < 2 * F || ldo < F) return mlxb_fail(MLXB_BAD_ARG, "gated_unit: %d columns, strides %d / %d", F, ldi, ldo);
+  const long long total = (long long)n_rows * F;
+  const int threads = 256;
+  const dim3 grid((unsigned)((total + threads - 1) / threads));
+  if (dtype == MLXB_F32)
+    launch_pdl(gated_unit_kernel<float>, grid, dim3(threads), 0, stream, (const float*)in, ldi, (float*)out, ldo, F, n_rows);
+  else if (dtype == MLXB_BF16)
+    launch_pdl(gated_unit_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)in, ldi,
+               (__nv_bfloat16*)out, ldo, F, n_rows);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "gated_unit: dtype code %d", dtype);
+  return mlxb_check_launch("gated_unit");
+}
+
+template <typename T>
+__global__ void scale_by_rows_kernel(const T* in, int ldi, const int* __restrict__ index, const T* __restrict__ table,
+                                     int ldt, int n_table_rows, int first, T* __restrict__ out, int ldo, int F, int n,
+                                     int* __restrict__ status) {
+  pdl_trigger();
+  pdl_wait();
+  in = after_wait(in);
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * F) return;
+  const int t = (int)(idx / F), j = (int)(idx - (long long)t * F);
+  const int id = index[t];
+  float e = 0.f;
+  if (id < 0 || id >= n_table_rows) { if (j == 0) atomicOr(status, MLXB_ST_TOKEN_RANGE); }
+  else e = to_f(table[(size_t)id * ldt + first + j]);
+  out[(size_t)t * ldo + j] = from_f<T>(to_f(in[(size_t)t * ldi + j]) * e);
+}
+
+MLXB_EXPORT int mlxb_scale_by_rows(int dtype, const void* in, int ldi, const int* index, const void* table, int ldt,
+                                   int n_table_rows, int first, void* out, int ldo, int F, int n_rows, int* status,
+                                   cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (F <= 0 || ldi < F || ldo < F || first < 0 || first + F > ldt)
+    return mlxb_fail(MLXB_BAD_ARG, "scale_by_rows: columns %d..%d of %d, strides %d / %d", first, first + F, ldt, ldi, ldo);
+  const long long total = (long long)n_rows * F;
+  const int threads = 256;
+  const dim3 grid((unsigned)((total + threads - 1) / threads));
+  if (dtype == MLXB_F32)
+    launch_pdl(scale_by_rows_kernel<float>, grid, dim3(threads), 0, stream, (const float*)in, ldi, index,
+               (const float*)table, ldt, n_table_rows, first, (float*)out, ldo, F, n_rows, status);
+  else if (dtype == MLXB_BF16)
+    launch_pdl(scale_by_rows_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)in, ldi, index,
+               (const __nv_bfloat16*)table, ldt, n_table_rows, first, (__nv_bfloat16*)out, ldo, F, n_rows, status);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "scale_by_rows: dtype code %d", dtype);
+  return mlxb_check_launch("scale_by_rows");
+}
+
+template <typename T>
+__global__ void join_rows_kernel(const float* a, const float* b, int D, T* __restrict__ out, int ldo, int n) {
+  pdl_trigger();
+  pdl_wait();
+  a = after_wait(a);
+  b = after_wait(b);
+  const int W = b ? 2 * D : D;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * W) return;
+  const int t = (int)(idx / W), j = (int)(idx - (long long)t * W);
+  const float v = j < D ? a[(size_t)t * D + j] : b[(size_t)t * D + j - D];
+  out[(size_t)t * ldo + j] = from_f<T>(v);
+}
+
+// a, b: float32 [n_rows, D] contiguous (b may be null); out: [n_rows, D or 2D] at row stride ldo.
+MLXB_EXPORT int mlxb_join_rows(int dtype, const float* a, const float* b, int D, void* out, int ldo, int n_rows,
+                               cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  const int W = b ? 2 * D : D;
+  if (D <= 0 || ldo < W) return mlxb_fail(MLXB_BAD_ARG, "join_rows: width %d into stride %d", W, ldo);
+  const long long total = (long long)n_rows * W;
+  const int threads = 256;
+  const dim3 grid((unsigned)((total + threads - 1) / threads));
+  if (dtype == MLXB_F32)
+    launch_pdl(join_rows_kernel<float>, grid, dim3(threads), 0, stream, a, b, D, (float*)out, ldo, n_rows);
+  else if (dtype == MLXB_BF16)
+    launch_pdl(join_rows_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, a, b, D, (__nv_bfloat16*)out, ldo, n_rows);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "join_rows: dtype code %d", dtype);
+  return mlxb_check_launch("join_rows");
+}

@@ -8,10 +8,10 @@
 
 MLXB_DEFINE_LAST_ERROR()
 
-template <typename T>
+template <typename T, typename TO = T>
 __global__ void embed_pos_kernel(const int* __restrict__ tok, const int* __restrict__ pos,
                                  const T* __restrict__ wte, const T* __restrict__ wpe,
-                                 T* __restrict__ out, int D, int V, int P, float scale,
+                                 TO* __restrict__ out, int D, int V, int P, float scale,
                                  int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
@@ -21,9 +21,9 @@ __global__ void embed_pos_kernel(const int* __restrict__ tok, const int* __restr
   bool ok = true;
   if (id < 0 || id >= V) { ok = false; if (threadIdx.x == 0) atomicOr(status, MLXB_ST_TOKEN_RANGE); }
   if (wpe && (p < 0 || p >= P)) { ok = false; if (threadIdx.x == 0) atomicOr(status, MLXB_ST_POSITION_RANGE); }
-  T* o = out + (size_t)t * D;
+  TO* o = out + (size_t)t * D;
   if (!ok) {
-    for (int d = threadIdx.x; d < D; d += blockDim.x) o[d] = from_f<T>(0.f);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) o[d] = from_f<TO>(0.f);
     return;
   }
   const T* e = wte + (size_t)id * D;
@@ -31,18 +31,23 @@ __global__ void embed_pos_kernel(const int* __restrict__ tok, const int* __restr
   for (int d = threadIdx.x; d < D; d += blockDim.x) {
     float v = to_f(e[d]) * scale;
     if (q) v += to_f(q[d]);
-    o[d] = from_f<T>(v);
+    o[d] = from_f<TO>(v);
   }
 }
 
-// dtype: MLXB_F32 / MLXB_BF16 for tables and output alike.
+// dtype: MLXB_F32 / MLXB_BF16 for the tables; the output has that dtype too, or is float32 with out_f32 (a model
+// whose residual stream is float32 whatever its weights are).
 MLXB_EXPORT int mlxb_embed_pos(int dtype, const int* tok, const int* pos, const void* wte, const void* wpe,
                                void* out, int T_, int D, int V, int P, float scale, int* status,
-                               cudaStream_t stream) {
+                               cudaStream_t stream, int out_f32) {
   if (T_ <= 0) return 0;
   if (D <= 0 || V <= 0) return mlxb_fail(MLXB_BAD_ARG, "embed_pos: width %d, vocabulary %d", D, V);
   const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : 64);
-  if (dtype == MLXB_F32)
+  if (dtype == MLXB_BF16 && out_f32)
+    embed_pos_kernel<__nv_bfloat16, float><<<T_, threads, 0, stream>>>(tok, pos, (const __nv_bfloat16*)wte,
+                                                                       (const __nv_bfloat16*)wpe, (float*)out, D, V, P,
+                                                                       scale, status);
+  else if (dtype == MLXB_F32)
     embed_pos_kernel<float><<<T_, threads, 0, stream>>>(tok, pos, (const float*)wte, (const float*)wpe,
                                                         (float*)out, D, V, P, scale, status);
   else if (dtype == MLXB_BF16)

@@ -1,7 +1,7 @@
 // Generic linear layer on the CUDA cores, true 32-bit arithmetic:
 //   C[M,N] = epilogue(A[M,K] . W[N,K]^T + bias[N]) (+ residual[M,N])
-// A, W and the residual are float32 or bfloat16 (one dtype for the three);
-// products and sums are float32 FMAs; C is that dtype or float32.
+// A and W are float32 or bfloat16 (one dtype for both); products and sums are
+// float32 FMAs; C is that dtype or float32, and the residual has C's dtype.
 // Every output element is one accumulator that adds k = 0..K-1 in order, so
 // a row's result does not depend on how many other rows the call has.
 // This is the whole matrix path of the float32 engine, and the fallback of
@@ -17,7 +17,7 @@ constexpr int BM = 64, BN = 64, BK = 16;
 template <typename T, typename TO, int EPI>
 __global__ void __launch_bounds__(256)
 gemm_simt_kernel(const T* __restrict__ A, const T* __restrict__ W, const float* __restrict__ bias,
-                 const T* residual, TO* C, int M, int N, int K,
+                 const TO* residual, TO* C, int M, int N, int K,
                  int lda, int ldc) {
   __shared__ float sA[BK][BM + 4];
   __shared__ float sW[BK][BN + 4];
@@ -83,12 +83,12 @@ static int launch(const void* A, const void* W, const float* bias, const void* r
   dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
   return dispatch_activation(epi, [&](auto e) {
     launch_pdl(gemm_simt_kernel<T, TO, decltype(e)::value>, grid, dim3(256), 0, stream, (const T*)A, (const T*)W, bias,
-               (const T*)residual, (TO*)C, M, N, K, lda, ldc);
+               (const TO*)residual, (TO*)C, M, N, K, lda, ldc);
     return mlxb_check_launch("linear (generic)");
   });
 }
 
-// dtype: dtype of A, W, residual.  out_f32 != 0: C is float32 whatever dtype is.
+// dtype: dtype of A and W.  out_f32 != 0: C and the residual are float32 whatever dtype is.
 // lda: row stride of A in elements (>= K); ldc: row stride of C and residual.
 // bias (float32[N]) and residual may be null.
 MLXB_EXPORT int mlxb_linear_simt(int dtype, int out_f32, const void* A, const void* W, const float* bias,

@@ -1,7 +1,7 @@
 // Linear layer for few rows (decode steps): M <= 64 tokens against a weight
 // that has to be streamed from HBM once.
 //   C[M,N] = epilogue(A[M,K] . W[N,K]^T + bias[N]) (+ residual[M,N])
-// A, W, residual bfloat16; float32 accumulation; C bfloat16 or float32.
+// A, W bfloat16; float32 accumulation; C bfloat16 or float32, the residual has C's dtype.
 //
 // The kernel is bound by reading W, so it is organised around that stream:
 // a CTA owns 8*NW output features (rows of W) over the whole K; its 8 (or 16) warps
@@ -82,7 +82,7 @@ struct NormFold {
 template <int MT, int NW, int WARPS, typename TO, int EPI, bool SCATTER, bool FOLD>
 __global__ void __launch_bounds__(WARPS * 32, (sizeof(TO) == 4 && MT == 1 && WARPS == 8) ? 3 : 1)
 gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W,
-                   const float* __restrict__ bias, const __nv_bfloat16* residual, TO* C, int M, int N, int K,
+                   const float* __restrict__ bias, const TO* residual, TO* C, int M, int N, int K,
                    int lda, int ldc, KvScatter kv, NormFold fold) {
   extern __shared__ float part[];   // [WARPS][MT*NW*4][32], then with FOLD [WARPS][16*MT][2] sums of x and x^2
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -193,7 +193,7 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
       const int e = threadIdx.x + x * WARPS * 32;
       int m, n;
       elem_mn(e, m, n);
-      e_res[x] = (residual && e < PER * 32 && m < M && n < N) ? __bfloat162float(residual[(size_t)m * ldc + n]) : 0.f;
+      e_res[x] = (residual && e < PER * 32 && m < M && n < N) ? to_f(residual[(size_t)m * ldc + n]) : 0.f;
     }
   }
 
@@ -331,7 +331,7 @@ gemm_smallm_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
       const bool in = e < PER * 32 && m < M && n < N;
       l_bias[x] = (in && bias) ? bias[n] : 0.f;
       l_colsum[x] = (FOLD && in) ? fold.colsum[n] : 0.f;
-      l_res[x] = (in && residual) ? __bfloat162float(residual[(size_t)m * ldc + n]) : 0.f;
+      l_res[x] = (in && residual) ? to_f(residual[(size_t)m * ldc + n]) : 0.f;
     }
 #pragma unroll
     for (int x = 0; x < EPT; ++x) {
@@ -374,7 +374,7 @@ static int launch_epi(const void* A, const void* W, const float* bias, const voi
       raised = true;
     }
     launch_pdl(kern, grid, dim3(WARPS * 32), smem, stream, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, bias,
-               (const __nv_bfloat16*)residual, (TO*)C, M, N, K, lda, ldc, kv, fold);
+               (const TO*)residual, (TO*)C, M, N, K, lda, ldc, kv, fold);
     return mlxb_check_launch("linear (few rows)");
   });
 }

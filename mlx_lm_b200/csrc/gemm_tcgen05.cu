@@ -1,6 +1,6 @@
 // Linear layer for many rows (prompt portions) on the 5th-generation tensor cores:
 //   C[M,N] = epilogue(A[M,K] . W[N,K]^T + bias[N]) (+ residual[M,N])
-// A, W, residual bfloat16 (both operands K-major: the K index is contiguous), C bfloat16 or float32.
+// A, W bfloat16 (both operands K-major: the K index is contiguous), C bfloat16 or float32, the residual has C's dtype.
 //
 // The kernel is persistent: one CTA per SM walks over the 128 x BN output tiles (BN = 128, 192 or 256,
 // chosen so that the last wave of tiles is as full as possible).  Warp 0 is the TMA producer: it fills a
@@ -484,7 +484,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 #define FETCH_RESIDUAL(C0, D0, D1, D2, D3, HAVE)                                                        \
       {                                                                                                   \
         HAVE = 0;                                                                                         \
-        if (residual != nullptr && m < M) {                                                               \
+        if (sizeof(TO) == 2 && residual != nullptr && m < M) {                                            \
           const int nb = n0 + half * HALF_COLS + (C0);                                                    \
           const __nv_bfloat16* rp = residual + row + nb;                                                  \
           const bool al = ((row + nb) & 7) == 0;                                                          \
@@ -535,8 +535,18 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
               const int n8 = n0 + half * HALF_COLS + c0 + g8 * 8;
               if (c0 + g8 * 8 < HALF_COLS && n8 < N) {
                 float v[8];
-                finish8<EPI>(v, r + g8 * 8, n8, N, row, bias, bias_vec, residual, (have >> g8) & 1,
-                             g8 == 0 ? res0 : (g8 == 1 ? res1 : (g8 == 2 ? res2 : res3)), fold.colsum, mean, rstd);
+                finish8<EPI>(v, r + g8 * 8, n8, N, row, bias, bias_vec, nullptr, false, res0, fold.colsum, mean, rstd);
+                if (residual != nullptr) {   // a float32 result takes a float32 residual
+                  const float* rf = reinterpret_cast<const float*>(residual) + row + n8;
+                  if (n8 + 8 <= N && ((row + n8) & 3) == 0) {
+                    const float4 a = *reinterpret_cast<const float4*>(rf), b = *reinterpret_cast<const float4*>(rf + 4);
+                    v[0] += a.x; v[1] += a.y; v[2] += a.z; v[3] += a.w; v[4] += b.x; v[5] += b.y; v[6] += b.z; v[7] += b.w;
+                  } else {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i)
+                      if (n8 + i < N) v[i] += rf[i];
+                  }
+                }
                 store8_f32(v, n8, N, row, reinterpret_cast<float*>(C));
               }
             }
@@ -735,7 +745,7 @@ static TileChoice tile_choice(int M, int N, int K, bool pairs_built) {
   return best;
 }
 
-// A: bfloat16 [M, K] at row stride lda; W: bfloat16 [N, K] contiguous; bias float32[N] or null; residual bfloat16
+// A: bfloat16 [M, K] at row stride lda; W: bfloat16 [N, K] contiguous; bias float32[N] or null; residual of C's dtype
 // [M, N] at row stride ldc or null (may alias C); C bfloat16 or float32 (out_f32) [M, N] at row stride ldc.
 // K, lda multiples of 8; A and W 16-byte aligned.  status: int32 word that receives MLXB_ST_WAIT_TIMEOUT if a
 // bounded wait inside the kernel gives up.

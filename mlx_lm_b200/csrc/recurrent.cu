@@ -1,0 +1,394 @@
+// Layers with a state of fixed size per request: short causal convolutions, the selective
+// state-space scan (Mamba-2) and the gated delta rule.  A step brings each request's next tokens as
+// a run of rows (req_first_token[r] .. , as many as carry the request's index in token_req); the state
+// of request r lives in row slots[r] of a float32 pool, is read at the start of the run and written
+// back at its end, so a sequence may be cut into steps anywhere.  All state and everything that feeds
+// a recurrence (step sizes, decays, gates, unit norms) is float32; inputs arrive in the activation
+// dtype.  The order of additions for a token depends on the layer's sizes only, never on the batch.
+//
+// conv_silu          out[t, c] = silu(bias[c] + sum_j w[c, taps-1-j] * in(t - j, c)),  j = 0 .. taps-1,
+//                    where in(t - j) is a row of this step if the run reaches that far back, else one of
+//                    the request's last taps-1 inputs kept in the state (zeros before the sequence starts).
+// conv_state_update  moves the last taps-1 inputs of every run into the state (launched after conv_silu).
+// mamba2_scan        per (request, head): S <- exp(-exp(A_log) dt) S + dt B x^T,  y = S^T C + D x,
+//                    dt = softplus(dt_raw + dt_bias); S is [N, V].
+// gated_delta_scan   per (request, head): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with
+//                    q and k divided by sqrt(|.|^2 + 1e-6) (q also by sqrt(dim)), beta = sigmoid(b_raw),
+//                    g = exp(-exp(A_log) softplus(a_raw + dt_bias)); S is [K, V].
+//
+// Both scans give a thread one column v of the state and every NS-th row of it (at most 16 values in
+// registers); the NS threads of a column are neighbouring lanes and add their partial sums by shuffles.
+// The inputs of 16 tokens at a time are staged in shared memory by the whole block.
+#include "common.cuh"
+
+MLXB_DEFINE_LAST_ERROR()
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+// Rows t0 .. t1-1 that belong to request r (they come first in the range).  Every thread of the block calls it.
+__device__ __forceinline__ int request_rows(const int* __restrict__ token_req, int t0, int t1, int r) {
+  int n = 0;
+  for (int base = t0; base < t1; base += blockDim.x) {
+    const int t = base + threadIdx.x;
+    n += __syncthreads_count(t < t1 && token_req[t] == r);
+  }
+  return n;
+}
+
+// ---------------------------------------------------------------- short convolution
+
+template <typename T>
+__global__ void conv_silu_kernel(const T* in, int ldi, const float* __restrict__ w, const float* __restrict__ bias,
+                                 int taps, int C, const float* state, const int* __restrict__ slots,
+                                 const int* __restrict__ positions, const int* __restrict__ token_req,
+                                 const int* __restrict__ req_first_position, T* __restrict__ out, int ldo) {
+  pdl_trigger();
+  const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int r = token_req[t];
+  if (r < 0 || c >= C) return;
+  const int i = positions[t] - req_first_position[r];   // rows of this run before t
+  const int slot = slots[r];
+  pdl_wait();
+  in = after_wait(in);
+  state = after_wait(state);
+  float acc = bias ? bias[c] : 0.f;
+  for (int j = 0; j < taps; ++j) {
+    float v;
+    if (j <= i) v = to_f(in[(size_t)(t - j) * ldi + c]);
+    else v = state[((size_t)slot * (taps - 1) + (taps - 1 + i - j)) * C + c];
+    acc = fmaf(w[(size_t)c * taps + taps - 1 - j], v, acc);
+  }
+  out[(size_t)t * ldo + c] = from_f<T>(silu_f(acc));
+}
+
+template <typename T>
+__global__ void conv_state_update_kernel(const T* in, int ldi, int taps, int C, float* state,
+                                         const int* __restrict__ slots, const int* __restrict__ token_req,
+                                         const int* __restrict__ req_first_token) {
+  pdl_trigger();
+  pdl_wait();
+  in = after_wait(in);
+  const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
+  const int t0 = req_first_token[r], t1 = req_first_token[r + 1];
+  const int n = request_rows(token_req, t0, t1, r);
+  if (n == 0 || c >= C) return;
+  const int keep = taps - 1;
+  float* st = state + (size_t)slots[r] * keep * C + c;
+  float nv[8];
+#pragma unroll
+  for (int s = 0; s < 8; ++s) {
+    if (s < keep) {
+      const int li = n - keep + s;
+      nv[s] = li >= 0 ? to_f(in[(size_t)(t0 + li) * ldi + c]) : st[(size_t)(s + n) * C];
+    }
+  }
+#pragma unroll
+  for (int s = 0; s < 8; ++s)
+    if (s < keep) st[(size_t)s * C] = nv[s];
+}
+
+template <typename T>
+static int conv_launch(const void* in, int ldi, const float* w, const float* bias, int taps, int C, float* state,
+                       const int* slots, const int* positions, const int* token_req, const int* req_first_token,
+                       const int* req_first_position, void* out, int ldo, int n_tokens, int n_requests,
+                       cudaStream_t stream) {
+  const int threads = 128;
+  launch_pdl(conv_silu_kernel<T>, dim3((C + threads - 1) / threads, n_tokens), dim3(threads), 0, stream, (const T*)in,
+             ldi, w, bias, taps, C, (const float*)state, slots, positions, token_req, req_first_position, (T*)out, ldo);
+  if (int e = mlxb_check_launch("conv_silu")) return e;
+  launch_pdl(conv_state_update_kernel<T>, dim3((C + threads - 1) / threads, n_requests), dim3(threads), 0, stream,
+             (const T*)in, ldi, taps, C, state, slots, token_req, req_first_token);
+  return mlxb_check_launch("conv_state_update");
+}
+
+// in: [n_tokens, >= C] at row stride ldi (activation dtype); w: float32 [C, taps]; bias: float32 [C] or null;
+// state: float32 [slots, taps-1, C]; out: [n_tokens, C] at row stride ldo.  Two launches: the convolution, then the
+// state's update (which must not overtake the convolution's reads of the state).
+MLXB_EXPORT int mlxb_conv_silu(int dtype, const void* in, int ldi, const float* w, const float* bias, int taps, int C,
+                               float* state, const int* slots, const int* positions, const int* token_req,
+                               const int* req_first_token, const int* req_first_position, void* out, int ldo,
+                               int n_tokens, int n_requests, cudaStream_t stream) {
+  if (n_tokens <= 0 || n_requests <= 0) return 0;
+  if (taps < 2 || taps > 9 || C <= 0 || ldi < C || ldo < C || n_tokens > 65535 * 32 || n_requests > 65535)
+    return mlxb_fail(MLXB_BAD_ARG, "conv: %d taps (2..9), %d channels, strides %d / %d, %d tokens of %d requests", taps, C,
+                     ldi, ldo, n_tokens, n_requests);
+  if (n_tokens > 65535) return mlxb_fail(MLXB_BAD_ARG, "conv: %d tokens are too many for one call", n_tokens);
+  if (dtype == MLXB_F32)
+    return conv_launch<float>(in, ldi, w, bias, taps, C, state, slots, positions, token_req, req_first_token,
+                              req_first_position, out, ldo, n_tokens, n_requests, stream);
+  if (dtype == MLXB_BF16)
+    return conv_launch<__nv_bfloat16>(in, ldi, w, bias, taps, C, state, slots, positions, token_req, req_first_token,
+                                      req_first_position, out, ldo, n_tokens, n_requests, stream);
+  return mlxb_fail(MLXB_BAD_DTYPE, "conv: dtype code %d", dtype);
+}
+
+// ---------------------------------------------------------------- scans
+
+constexpr int SCAN_NPT = 16;     // rows of a state column a thread holds
+constexpr int SCAN_CHUNK = 16;   // tokens staged at a time
+
+struct ScanShape {
+  int NS, VB, threads, zblocks;
+};
+
+// n_rows: rows of the state (N or K); V: its columns.
+static inline ScanShape scan_shape(int n_rows, int V) {
+  ScanShape s;
+  s.NS = 1;
+  while (s.NS * SCAN_NPT < n_rows) s.NS <<= 1;
+  const int lanes = 32 / s.NS;                       // columns per warp
+  const int vmax = 512 / s.NS;                       // columns per block at most
+  int vb = (V + lanes - 1) / lanes * lanes;
+  if (vb > vmax) vb = vmax;
+  s.VB = vb;
+  s.threads = vb * s.NS;
+  s.zblocks = (V + vb - 1) / vb;
+  return s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+mamba2_scan_kernel(const T* xbc, int ldx, int x_off, int b_off, int c_off, const T* dt_raw, int lddt,
+                   const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                   const float* __restrict__ Dskip, float* state, const int* __restrict__ slots,
+                   const int* __restrict__ token_req, const int* __restrict__ req_first_token, float* __restrict__ y,
+                   int ldy, int H, int G, int N, int V, int NS, int VB) {
+  extern __shared__ float sm[];
+  float* sB = sm;                          // [CHUNK][N]
+  float* sC = sB + SCAN_CHUNK * N;         // [CHUNK][N]
+  float* sx = sC + SCAN_CHUNK * N;         // [CHUNK][VB]
+  float* sdt = sx + SCAN_CHUNK * VB;       // [CHUNK]
+  float* sa = sdt + SCAN_CHUNK;            // [CHUNK]
+  pdl_trigger();
+  const int h = blockIdx.x, r = blockIdx.y, vb = blockIdx.z;
+  const int t0 = req_first_token[r], t1 = req_first_token[r + 1];
+  pdl_wait();
+  xbc = after_wait(xbc);
+  dt_raw = after_wait(dt_raw);
+  const int n = request_rows(token_req, t0, t1, r);
+  if (n == 0) return;
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int s = tid % NS, vl = tid / NS, v = vb * VB + vl;
+  const bool valid = v < V;
+  const int g = h / (H / G);
+  float* st = state + ((size_t)slots[r] * H + h) * N * V;
+  float S[SCAN_NPT];
+#pragma unroll
+  for (int i = 0; i < SCAN_NPT; ++i) {
+    const int nn = s + i * NS;
+    S[i] = (valid && nn < N) ? st[(size_t)nn * V + v] : 0.f;
+  }
+  const float negA = -expf(A_log[h]), skip = Dskip[h], bias = dt_bias[h];
+  for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
+    const int nc = min(SCAN_CHUNK, n - c0);
+    __syncthreads();
+    for (int idx = tid; idx < nc * N; idx += nthreads) {
+      const int tt = idx / N, nn = idx - tt * N;
+      const T* row = xbc + (size_t)(t0 + c0 + tt) * ldx;
+      sB[idx] = to_f(row[b_off + g * N + nn]);
+      sC[idx] = to_f(row[c_off + g * N + nn]);
+    }
+    for (int idx = tid; idx < nc * VB; idx += nthreads) {
+      const int tt = idx / VB, vv = idx - tt * VB, col = vb * VB + vv;
+      sx[idx] = col < V ? to_f(xbc[(size_t)(t0 + c0 + tt) * ldx + x_off + h * V + col]) : 0.f;
+    }
+    if (tid < nc) {
+      const float d = softplus_f(to_f(dt_raw[(size_t)(t0 + c0 + tid) * lddt + h]) + bias);
+      sdt[tid] = d;
+      sa[tid] = expf(negA * d);
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nc; ++tt) {
+      const float a = sa[tt], xv = sx[tt * VB + vl], dtx = sdt[tt] * xv;
+      const float* Bt = sB + tt * N;
+      const float* Ct = sC + tt * N;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < SCAN_NPT; ++i) {
+        const int nn = s + i * NS;
+        if (nn < N) {
+          S[i] = fmaf(a, S[i], dtx * Bt[nn]);
+          acc = fmaf(S[i], Ct[nn], acc);
+        }
+      }
+      for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+      if (s == 0 && valid) y[(size_t)(t0 + c0 + tt) * ldy + h * V + v] = fmaf(skip, xv, acc);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < SCAN_NPT; ++i) {
+    const int nn = s + i * NS;
+    if (valid && nn < N) st[(size_t)nn * V + v] = S[i];
+  }
+}
+
+// xbc: the convolution's output [n_tokens, ...] (activation dtype) holding x (H*V columns from x_off), B and C (G*N
+// columns each from b_off / c_off); dt_raw: [n_tokens, >= H] at row stride lddt; state: float32 [slots, H, N, V];
+// y: float32 [n_tokens, H*V] at row stride ldy.
+MLXB_EXPORT int mlxb_mamba2_scan(int dtype, const void* xbc, int ldx, int x_off, int b_off, int c_off,
+                                 const void* dt_raw, int lddt, const float* dt_bias, const float* A_log,
+                                 const float* Dskip, float* state, const int* slots, const int* token_req,
+                                 const int* req_first_token, float* y, int ldy, int H, int G, int N, int V,
+                                 int n_requests, cudaStream_t stream) {
+  if (n_requests <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || N <= 0 || V <= 0 || N > 32 * SCAN_NPT || n_requests > 65535)
+    return mlxb_fail(MLXB_BAD_ARG, "mamba2_scan: %d heads in %d groups, state %d x %d (at most %d rows)", H, G, N, V,
+                     32 * SCAN_NPT);
+  const ScanShape sh = scan_shape(N, V);
+  const size_t smem = (size_t)(SCAN_CHUNK * (2 * N + sh.VB + 2)) * sizeof(float);
+  const dim3 grid(H, n_requests, sh.zblocks);
+  cudaError_t e = cudaSuccess;
+  if (dtype == MLXB_F32) {
+    if (smem > 48 * 1024) e = cudaFuncSetAttribute(mamba2_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      launch_pdl(mamba2_scan_kernel<float>, grid, dim3(sh.threads), smem, stream, (const float*)xbc, ldx, x_off, b_off,
+                 c_off, (const float*)dt_raw, lddt, dt_bias, A_log, Dskip, state, slots, token_req, req_first_token, y,
+                 ldy, H, G, N, V, sh.NS, sh.VB);
+  } else if (dtype == MLXB_BF16) {
+    if (smem > 48 * 1024) e = cudaFuncSetAttribute(mamba2_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      launch_pdl(mamba2_scan_kernel<__nv_bfloat16>, grid, dim3(sh.threads), smem, stream, (const __nv_bfloat16*)xbc, ldx,
+                 x_off, b_off, c_off, (const __nv_bfloat16*)dt_raw, lddt, dt_bias, A_log, Dskip, state, slots,
+                 token_req, req_first_token, y, ldy, H, G, N, V, sh.NS, sh.VB);
+  } else {
+    return mlxb_fail(MLXB_BAD_DTYPE, "mamba2_scan: dtype code %d", dtype);
+  }
+  if (e != cudaSuccess) return mlxb_fail((int)e, "mamba2_scan: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  return mlxb_check_launch("mamba2_scan");
+}
+
+template <typename T>
+__global__ void __launch_bounds__(512)
+gated_delta_scan_kernel(const T* qkv, int ldq, int q_off, int k_off, int v_off, const T* b_raw, int ldb,
+                        const T* a_raw, int lda, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
+                        float* state, const int* __restrict__ slots, const int* __restrict__ token_req,
+                        const int* __restrict__ req_first_token, float* __restrict__ o, int ldo, int H, int G, int K,
+                        int V, int NS, int VB) {
+  extern __shared__ float sm[];
+  float* sq = sm;                          // [CHUNK][K]
+  float* sk = sq + SCAN_CHUNK * K;         // [CHUNK][K]
+  float* sv = sk + SCAN_CHUNK * K;         // [CHUNK][VB]
+  float* sbeta = sv + SCAN_CHUNK * VB;     // [CHUNK]
+  float* sg = sbeta + SCAN_CHUNK;          // [CHUNK]
+  pdl_trigger();
+  const int h = blockIdx.x, r = blockIdx.y, vb = blockIdx.z;
+  const int t0 = req_first_token[r], t1 = req_first_token[r + 1];
+  pdl_wait();
+  qkv = after_wait(qkv);
+  b_raw = after_wait(b_raw);
+  a_raw = after_wait(a_raw);
+  const int n = request_rows(token_req, t0, t1, r);
+  if (n == 0) return;
+  const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
+  const int s = tid % NS, vl = tid / NS, v = vb * VB + vl;
+  const bool valid = v < V;
+  const int g = h / (H / G);
+  float* st = state + ((size_t)slots[r] * H + h) * K * V;
+  float S[SCAN_NPT];
+#pragma unroll
+  for (int i = 0; i < SCAN_NPT; ++i) {
+    const int kk = s + i * NS;
+    S[i] = (valid && kk < K) ? st[(size_t)kk * V + v] : 0.f;
+  }
+  const float negA = -expf(A_log[h]), bias = dt_bias[h], q_scale = 1.f / sqrtf((float)K);
+  for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
+    const int nc = min(SCAN_CHUNK, n - c0);
+    __syncthreads();
+    for (int tt = warp; tt < nc; tt += nwarps) {     // a warp per token: load q and k of the head, make them unit vectors
+      const T* row = qkv + (size_t)(t0 + c0 + tt) * ldq;
+      float q2 = 0.f, k2 = 0.f;
+      for (int kk = lane; kk < K; kk += 32) {
+        const float qv = to_f(row[q_off + g * K + kk]), kv = to_f(row[k_off + g * K + kk]);
+        sq[tt * K + kk] = qv;
+        sk[tt * K + kk] = kv;
+        q2 = fmaf(qv, qv, q2);
+        k2 = fmaf(kv, kv, k2);
+      }
+      q2 = warp_sum(q2);
+      k2 = warp_sum(k2);
+      const float rq = q_scale / sqrtf(q2 + 1e-6f), rk = 1.f / sqrtf(k2 + 1e-6f);
+      for (int kk = lane; kk < K; kk += 32) {
+        sq[tt * K + kk] *= rq;
+        sk[tt * K + kk] *= rk;
+      }
+    }
+    for (int idx = tid; idx < nc * VB; idx += nthreads) {
+      const int tt = idx / VB, vv = idx - tt * VB, col = vb * VB + vv;
+      sv[idx] = col < V ? to_f(qkv[(size_t)(t0 + c0 + tt) * ldq + v_off + h * V + col]) : 0.f;
+    }
+    if (tid < nc) {
+      const size_t row = (size_t)(t0 + c0 + tid);
+      sbeta[tid] = 1.f / (1.f + expf(-to_f(b_raw[row * ldb + h])));
+      sg[tid] = expf(negA * softplus_f(to_f(a_raw[row * lda + h]) + bias));
+    }
+    __syncthreads();
+    for (int tt = 0; tt < nc; ++tt) {
+      const float gg = sg[tt], beta = sbeta[tt], vv = sv[tt * VB + vl];
+      const float* kt = sk + tt * K;
+      const float* qt = sq + tt * K;
+      float acc = 0.f;
+#pragma unroll
+      for (int i = 0; i < SCAN_NPT; ++i) {
+        const int kk = s + i * NS;
+        if (kk < K) {
+          S[i] *= gg;
+          acc = fmaf(S[i], kt[kk], acc);
+        }
+      }
+      for (int w = NS >> 1; w > 0; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+      const float u = beta * (vv - acc);
+      float out = 0.f;
+#pragma unroll
+      for (int i = 0; i < SCAN_NPT; ++i) {
+        const int kk = s + i * NS;
+        if (kk < K) {
+          S[i] = fmaf(kt[kk], u, S[i]);
+          out = fmaf(S[i], qt[kk], out);
+        }
+      }
+      for (int w = NS >> 1; w > 0; w >>= 1) out += __shfl_xor_sync(0xffffffffu, out, w);
+      if (s == 0 && valid) o[(size_t)(t0 + c0 + tt) * ldo + h * V + v] = out;
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < SCAN_NPT; ++i) {
+    const int kk = s + i * NS;
+    if (valid && kk < K) st[(size_t)kk * V + v] = S[i];
+  }
+}
+
+// qkv: the convolutions' output [n_tokens, ...] (activation dtype): q and k (G*K columns each from q_off / k_off),
+// v (H*V columns from v_off); b_raw, a_raw: [n_tokens, >= H] at row strides ldb / lda; state: float32 [slots, H, K, V];
+// o: float32 [n_tokens, H*V] at row stride ldo.
+MLXB_EXPORT int mlxb_gated_delta_scan(int dtype, const void* qkv, int ldq, int q_off, int k_off, int v_off,
+                                      const void* b_raw, int ldb, const void* a_raw, int lda, const float* dt_bias,
+                                      const float* A_log, float* state, const int* slots, const int* token_req,
+                                      const int* req_first_token, float* o, int ldo, int H, int G, int K, int V,
+                                      int n_requests, cudaStream_t stream) {
+  if (n_requests <= 0) return 0;
+  if (H <= 0 || G <= 0 || H % G || K <= 0 || V <= 0 || K > 32 * SCAN_NPT || n_requests > 65535)
+    return mlxb_fail(MLXB_BAD_ARG, "gated_delta_scan: %d heads over %d key heads, state %d x %d (at most %d rows)", H, G,
+                     K, V, 32 * SCAN_NPT);
+  const ScanShape sh = scan_shape(K, V);
+  const size_t smem = (size_t)(SCAN_CHUNK * (2 * K + sh.VB + 2)) * sizeof(float);
+  const dim3 grid(H, n_requests, sh.zblocks);
+  cudaError_t e = cudaSuccess;
+  if (dtype == MLXB_F32) {
+    if (smem > 48 * 1024) e = cudaFuncSetAttribute(gated_delta_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      launch_pdl(gated_delta_scan_kernel<float>, grid, dim3(sh.threads), smem, stream, (const float*)qkv, ldq, q_off,
+                 k_off, v_off, (const float*)b_raw, ldb, (const float*)a_raw, lda, dt_bias, A_log, state, slots,
+                 token_req, req_first_token, o, ldo, H, G, K, V, sh.NS, sh.VB);
+  } else if (dtype == MLXB_BF16) {
+    if (smem > 48 * 1024) e = cudaFuncSetAttribute(gated_delta_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e == cudaSuccess)
+      launch_pdl(gated_delta_scan_kernel<__nv_bfloat16>, grid, dim3(sh.threads), smem, stream, (const __nv_bfloat16*)qkv,
+                 ldq, q_off, k_off, v_off, (const __nv_bfloat16*)b_raw, ldb, (const __nv_bfloat16*)a_raw, lda, dt_bias,
+                 A_log, state, slots, token_req, req_first_token, o, ldo, H, G, K, V, sh.NS, sh.VB);
+  } else {
+    return mlxb_fail(MLXB_BAD_DTYPE, "gated_delta_scan: dtype code %d", dtype);
+  }
+  if (e != cudaSuccess) return mlxb_fail((int)e, "gated_delta_scan: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
+  return mlxb_check_launch("gated_delta_scan");
+}

@@ -1,0 +1,128 @@
+// Root-mean-square norms over float32 rows, and the update of a float32 residual stream.
+//
+// rmsnorm          out[r, c] = x[row(r), c] / sqrt(mean_g(x^2) + eps) * (offset + w[c % period])
+//                  The row is cut into `groups` equal parts, each divided by its own root mean square.
+//                  The weight repeats with `period` columns (the width: one weight per column; the width
+//                  of a part: the parts share one weight), is stored as it is (offset 0) or as its distance
+//                  from one (offset 1).  A gate g (activation dtype) may come in: mode 1 multiplies x by
+//                  silu(g) BEFORE the statistics, mode 2 multiplies the normed value by silu(g).
+//                  x is float32; the result has the activation dtype.  All arithmetic is float32.
+// residual_update  x[r, :] += scale * (f1(y1[r, :]) + f2(y2[r, :])),  f_i = rmsnorm with weight w_i over the
+//                  whole row, or the identity where w_i is null; y2 may be null.  Optionally a copy of the new
+//                  row in the activation dtype is left in `cast_out` for the products that read it next.
+#include "common.cuh"
+
+MLXB_DEFINE_LAST_ERROR()
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* x, int ldx, const int* __restrict__ rows, int n_src_rows,
+                               const float* __restrict__ w, float offset, int period, const TO* gate, int ldg,
+                               int gate_mode, TO* __restrict__ out, int ldo, int D, int groups, float eps) {
+  __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
+  x = after_wait(x);
+  gate = after_wait(gate);
+  const int r = blockIdx.x, g = blockIdx.y;
+  const int src = rows ? rows[r] : r;
+  const int Dg = D / groups;
+  TO* o = out + (size_t)r * ldo + (size_t)g * Dg;
+  if (src < 0 || src >= n_src_rows) {
+    for (int c = threadIdx.x; c < Dg; c += blockDim.x) o[c] = from_f<TO>(0.f);
+    return;
+  }
+  const float* xr = x + (size_t)src * ldx + (size_t)g * Dg;
+  const TO* gr = gate ? gate + (size_t)src * ldg + (size_t)g * Dg : nullptr;
+  float s = 0.f;
+  for (int c = threadIdx.x; c < Dg; c += blockDim.x) {
+    float v = xr[c];
+    if (gate_mode == 1) v *= silu_f(to_f(gr[c]));
+    s = fmaf(v, v, s);
+  }
+  const float rinv = 1.f / sqrtf(block_sum(s, red) / (float)Dg + eps);
+  for (int c = threadIdx.x; c < Dg; c += blockDim.x) {
+    float v = xr[c];
+    if (gate_mode == 1) v *= silu_f(to_f(gr[c]));
+    v = v * rinv * (offset + w[(g * Dg + c) % period]);
+    if (gate_mode == 2) v *= silu_f(to_f(gr[c]));
+    o[c] = from_f<TO>(v);
+  }
+}
+
+MLXB_EXPORT int mlxb_rmsnorm(int out_dtype, const float* x, int ldx, const int* rows, int n_src_rows, const float* w,
+                             float offset, int period, const void* gate, int ldg, int gate_mode, void* out, int ldo,
+                             int R, int D, int groups, float eps, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (D <= 0 || groups <= 0 || D % groups || period <= 0 || ldx < D || ldo < D)
+    return mlxb_fail(MLXB_BAD_ARG, "rmsnorm: width %d in %d parts, weight period %d, strides %d / %d", D, groups, period,
+                     ldx, ldo);
+  if (gate_mode < 0 || gate_mode > 2 || ((gate_mode != 0) != (gate != nullptr)))
+    return mlxb_fail(MLXB_BAD_ARG, "rmsnorm: gate mode %d %s a gate", gate_mode, gate ? "with" : "without");
+  if (groups > 65535) return mlxb_fail(MLXB_BAD_ARG, "rmsnorm: %d parts", groups);
+  const int Dg = D / groups;
+  const int threads = Dg >= 2048 ? 256 : (Dg >= 512 ? 128 : (Dg >= 128 ? 64 : 32));
+  const dim3 grid(R, groups);
+  if (out_dtype == MLXB_F32)
+    launch_pdl(rmsnorm_kernel<float>, grid, dim3(threads), 0, stream, x, ldx, rows, n_src_rows, w, offset, period,
+               (const float*)gate, ldg, gate_mode, (float*)out, ldo, D, groups, eps);
+  else if (out_dtype == MLXB_BF16)
+    launch_pdl(rmsnorm_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, x, ldx, rows, n_src_rows, w, offset,
+               period, (const __nv_bfloat16*)gate, ldg, gate_mode, (__nv_bfloat16*)out, ldo, D, groups, eps);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "rmsnorm: dtype code %d", out_dtype);
+  return mlxb_check_launch("rmsnorm");
+}
+
+template <typename TO>
+__global__ void residual_update_kernel(float* x, int ldx, const float* y1, const float* __restrict__ w1,
+                                       const float* y2, const float* __restrict__ w2, int ldy, float scale, float eps,
+                                       TO* __restrict__ cast_out, int ldc, int D) {
+  __shared__ float red[33];
+  pdl_trigger();
+  pdl_wait();
+  x = after_wait(x);
+  y1 = after_wait(y1);
+  y2 = after_wait(y2);
+  const int r = blockIdx.x;
+  float* xr = x + (size_t)r * ldx;
+  const float* a = y1 + (size_t)r * ldy;
+  const float* b = y2 ? y2 + (size_t)r * ldy : nullptr;
+  float ra = 1.f, rb = 1.f;
+  if (w1) {
+    float s = 0.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) s = fmaf(a[c], a[c], s);
+    ra = 1.f / sqrtf(block_sum(s, red) / (float)D + eps);
+  }
+  if (b && w2) {
+    float s = 0.f;
+    for (int c = threadIdx.x; c < D; c += blockDim.x) s = fmaf(b[c], b[c], s);
+    rb = 1.f / sqrtf(block_sum(s, red) / (float)D + eps);
+  }
+  for (int c = threadIdx.x; c < D; c += blockDim.x) {
+    float v = w1 ? a[c] * ra * w1[c] : a[c];
+    if (b) v += w2 ? b[c] * rb * w2[c] : b[c];
+    const float nx = xr[c] + scale * v;
+    xr[c] = nx;
+    if (cast_out) cast_out[(size_t)r * ldc + c] = from_f<TO>(nx);
+  }
+}
+
+MLXB_EXPORT int mlxb_residual_update(int cast_dtype, float* x, int ldx, const float* y1, const float* w1,
+                                     const float* y2, const float* w2, int ldy, float scale, float eps, void* cast_out,
+                                     int ldc, int R, int D, cudaStream_t stream) {
+  if (R <= 0) return 0;
+  if (D <= 0 || ldx < D || ldy < D || y1 == nullptr || (cast_out && ldc < D))
+    return mlxb_fail(MLXB_BAD_ARG, "residual_update: width %d, strides %d / %d / %d", D, ldx, ldy, ldc);
+  const int threads = D >= 2048 ? 256 : (D >= 512 ? 128 : 64);
+  if (cast_dtype == MLXB_F32)
+    launch_pdl(residual_update_kernel<float>, dim3(R), dim3(threads), 0, stream, x, ldx, y1, w1, y2, w2, ldy, scale,
+               eps, (float*)cast_out, ldc, D);
+  else if (cast_dtype == MLXB_BF16)
+    launch_pdl(residual_update_kernel<__nv_bfloat16>, dim3(R), dim3(threads), 0, stream, x, ldx, y1, w1, y2, w2, ldy,
+               scale, eps, (__nv_bfloat16*)cast_out, ldc, D);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "residual_update: dtype code %d", cast_dtype);
+  return mlxb_check_launch("residual_update");
+}

@@ -1,0 +1,122 @@
+// Queries, keys and values on their way from the projection into the attention kernels:
+//   q, k   optional RMS norm over the WHOLE projection of a token (all heads at once, one weight per
+//          column, eps inside the root), then a rotation by position of the first 2*half dimensions of
+//          every head: dimension i is paired with i + half, the pair (u, v) at position p becomes
+//          (u cos a - v sin a, v cos a + u sin a) with a = p * freq[i]; the other dimensions pass.
+//   q      goes to a buffer [tokens, Hq*Dh]; k and v go into the token's page.  Heads are laid out Dh
+//          wide there: Dh >= max(dk, dv), the columns beyond a head's own size are written as zeros, so
+//          that attention kernels built for one head size serve keys and values of different sizes
+//          (zeros add nothing to a score, and the value columns they produce are never read).
+// Norm, angle, sine and cosine are float32 (the angle is the float32 product of the position and a
+// float32 frequency, reduced accurately by sincosf).
+#include "common.cuh"
+
+MLXB_DEFINE_LAST_ERROR()
+
+template <typename T>
+__global__ void qkv_prepare_kernel(const T* proj, int ld, int q_off, int k_off, int v_off, int Hq, int Hkv, int dk,
+                                   int dv, int Dh, const float* __restrict__ wq, const float* __restrict__ wk,
+                                   float eps, const float* __restrict__ freq, int half,
+                                   const int* __restrict__ positions, const int* __restrict__ token_req,
+                                   const int* __restrict__ block_table, int max_pages, int n_pages, int page,
+                                   T* __restrict__ q_out, int ldq, T* __restrict__ k_pool, T* __restrict__ v_pool,
+                                   int write, int* __restrict__ status) {
+  __shared__ float red[33];
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const int r = token_req[t];
+  if (r < 0) return;
+  const int p = positions[t];
+  long long slot = -1;      // element offset of the token's row in head 0 of its page
+  if (write) {
+    const int lp = p / page;
+    if (p < 0 || lp >= max_pages) {
+      if (threadIdx.x == 0) atomicOr(status, MLXB_ST_POSITION_RANGE);
+    } else {
+      const int pg = block_table[(size_t)r * max_pages + lp];
+      if (pg >= n_pages) {
+        if (threadIdx.x == 0) atomicOr(status, MLXB_ST_PAGE_RANGE);
+      } else if (pg >= 0) {
+        slot = ((long long)pg * Hkv * page + (p % page)) * Dh;
+      }
+    }
+  }
+  pdl_wait();
+  proj = after_wait(proj);
+  const T* row = proj + (size_t)t * ld;
+  float rq = 1.f, rk = 1.f;
+  if (wq) {
+    float s = 0.f;
+    for (int e = threadIdx.x; e < Hq * dk; e += blockDim.x) { const float v = to_f(row[q_off + e]); s = fmaf(v, v, s); }
+    rq = 1.f / sqrtf(block_sum(s, red) / (float)(Hq * dk) + eps);
+  }
+  if (wk) {
+    float s = 0.f;
+    for (int e = threadIdx.x; e < Hkv * dk; e += blockDim.x) { const float v = to_f(row[k_off + e]); s = fmaf(v, v, s); }
+    rk = 1.f / sqrtf(block_sum(s, red) / (float)(Hkv * dk) + eps);
+  }
+  const float fp = (float)p;
+  // one thread per (head, dimension below Dh) of q and of k; the lower partner of a pair computes both
+  for (int e = threadIdx.x; e < (Hq + Hkv) * Dh; e += blockDim.x) {
+    const int hh = e / Dh, i = e - hh * Dh;
+    const bool is_q = hh < Hq;
+    const int h = is_q ? hh : hh - Hq;
+    const int off = is_q ? q_off : k_off;
+    const float* w = is_q ? wq : wk;
+    const float rn = is_q ? rq : rk;
+    T* dst;
+    if (is_q) dst = q_out + (size_t)t * ldq + (size_t)h * Dh;
+    else if (slot >= 0) dst = k_pool + slot + (size_t)h * page * Dh;
+    else continue;
+    if (i >= dk) { dst[i] = from_f<T>(0.f); continue; }
+    if (i >= half && i < 2 * half) continue;      // written by its partner
+    const int c = h * dk + i;
+    float u = to_f(row[off + c]) * rn;
+    if (w) u *= w[c];
+    if (i < half) {
+      float v = to_f(row[off + c + half]) * rn;
+      if (w) v *= w[c + half];
+      float sn, cs;
+      sincosf(fp * freq[i], &sn, &cs);
+      dst[i] = from_f<T>(u * cs - v * sn);
+      dst[i + half] = from_f<T>(v * cs + u * sn);
+    } else {
+      dst[i] = from_f<T>(u);
+    }
+  }
+  if (slot >= 0) {
+    for (int e = threadIdx.x; e < Hkv * Dh; e += blockDim.x) {
+      const int h = e / Dh, i = e - h * Dh;
+      v_pool[slot + (size_t)h * page * Dh + i] = i < dv ? row[v_off + h * dv + i] : from_f<T>(0.f);
+    }
+  }
+}
+
+// proj: [n_tokens, ...] at row stride ld holding q (Hq*dk columns from q_off), k (Hkv*dk from k_off) and v (Hkv*dv
+// from v_off); wq / wk: float32 norm weights over the whole q / k projection, or null for no norm; freq: float32
+// [half] rotation frequencies (half may be 0); pools [n_pages, Hkv, page, Dh]; q_out [n_tokens, Hq*Dh] at row stride ldq.
+MLXB_EXPORT int mlxb_qkv_prepare(int dtype, const void* proj, int ld, int q_off, int k_off, int v_off, int Hq, int Hkv,
+                                 int dk, int dv, int Dh, const float* wq, const float* wk, float eps, const float* freq,
+                                 int half, const int* positions, const int* token_req, const int* block_table,
+                                 int max_pages, int n_pages, int page, void* q_out, int ldq, void* k_pool, void* v_pool,
+                                 int write, int n_tokens, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (Hq <= 0 || Hkv <= 0 || dk <= 0 || dv <= 0 || Dh < dk || Dh < dv || 2 * half > dk || half < 0 || page <= 0 ||
+      (half > 0 && freq == nullptr) || ldq < Hq * Dh)
+    return mlxb_fail(MLXB_BAD_ARG, "qkv_prepare: %d/%d heads, sizes %d/%d in %d, %d rotated pairs, page %d", Hq, Hkv, dk,
+                     dv, Dh, half, page);
+  const int work = (Hq + Hkv) * Dh;
+  const int threads = work >= 2048 ? 256 : (work >= 512 ? 128 : 64);
+  if (dtype == MLXB_F32)
+    launch_pdl(qkv_prepare_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)proj, ld, q_off, k_off,
+               v_off, Hq, Hkv, dk, dv, Dh, wq, wk, eps, freq, half, positions, token_req, block_table, max_pages, n_pages,
+               page, (float*)q_out, ldq, (float*)k_pool, (float*)v_pool, write, status);
+  else if (dtype == MLXB_BF16)
+    launch_pdl(qkv_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream, (const __nv_bfloat16*)proj,
+               ld, q_off, k_off, v_off, Hq, Hkv, dk, dv, Dh, wq, wk, eps, freq, half, positions, token_req, block_table,
+               max_pages, n_pages, page, (__nv_bfloat16*)q_out, ldq, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool,
+               write, status);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "qkv_prepare: dtype code %d", dtype);
+  return mlxb_check_launch("qkv_prepare");
+}

@@ -83,6 +83,19 @@ class LayerCacheView:
     page_size: int = 0
     state: Optional[torch.Tensor] = None         # [n_slots, *shape] float32
     slots: Optional[torch.Tensor] = None         # int32 [R] on the device
+    parts: Optional[Dict[str, "LayerCacheView"]] = None   # kind "several": the block's caches by name
+
+    def side(self, name: str) -> "LayerCacheView":
+        """One of a block's several caches: the one called ``name``, or, where names have dots
+        (``right.conv``, ``right.rule``), those under ``name.`` as a view of their own."""
+        if self.parts is None:
+            raise KeyError(f"this block has one cache, not several ({name!r})")
+        if name in self.parts:
+            return self.parts[name]
+        sub = {k[len(name) + 1:]: v for k, v in self.parts.items() if k.startswith(name + ".")}
+        if not sub:
+            raise KeyError(f"no cache named {name!r} among {sorted(self.parts)}")
+        return LayerCacheView("several", self.write, parts=sub)
 
 
 @dataclass
@@ -128,16 +141,25 @@ class StepContext:
 
     def cache_view(self, entry: RunEntry) -> LayerCacheView:
         mgr = self.engine.cache
+        names = mgr.names_of(entry.cache_id)
+        if names:
+            return LayerCacheView("several", entry.write,
+                                  parts={n: self._view_of((entry.cache_id, n), entry.write) for n in names})
         if entry.cache_id not in mgr._where:
             return LayerCacheView("none", write=False)
-        kind, gi = mgr.where(entry.cache_id)
+        return self._view_of(entry.cache_id, entry.write)
+
+    def _view_of(self, key, write: bool) -> LayerCacheView:
+        mgr = self.engine.cache
+        entry = RunEntry(0, write=write)
+        kind, gi = mgr.where(key)
         if kind == "kv":
             g = mgr.kv_groups[gi]
-            i = g.index_of(entry.cache_id)
+            i = g.index_of(key)
             return LayerCacheView("kv", entry.write, k=g.k[i], v=g.v[i], block_table=self._tables[gi],
                                   page_size=mgr.page_size)
         g = mgr.state_groups[gi]
-        return LayerCacheView("state", entry.write, state=g.data[g.index_of(entry.cache_id)], slots=self._slots)
+        return LayerCacheView("state", entry.write, state=g.data[g.index_of(key)], slots=self._slots)
 
     def gather_rows(self, x: torch.Tensor) -> torch.Tensor:
         """The rows of ``x`` whose logits are wanted, as a tensor of their own (what a final norm does on the
@@ -150,13 +172,16 @@ class StepContext:
 class Engine:
     """A model, its cache and the step function."""
 
+    DEFAULT_MAX_LEN = 8192
+
     def __init__(self, model: Model, page_size: int = 16, max_tokens: Optional[int] = None,
                  n_pages: Optional[int] = None, max_requests: int = 64, max_len: Optional[int] = None):
         ops.require_cuda()
         self.model = model
         d = model.description
         limit = d.max_positions
-        self.max_len = min(x for x in (max_len, limit, 1 << 20) if x is not None)
+        # a model without a limit of its own (rotated or no positions) gets DEFAULT_MAX_LEN unless the caller says more
+        self.max_len = min(x for x in (max_len, limit) if x is not None) if (max_len or limit) else self.DEFAULT_MAX_LEN
         if n_pages is None:
             if max_tokens is None:
                 max_tokens = max_requests * self.max_len

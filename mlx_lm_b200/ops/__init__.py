@@ -175,23 +175,26 @@ def _call(libname: str, fname: str, argtypes, *args) -> None:
 # embedding + position add
 
 _EMBED_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-               c_void_p, c_void_p]
+               c_void_p, c_void_p, c_int]
 
 
 def embed_pos(tokens, positions, wte, wpe, out, status, stream, scale: float = 1.0) -> None:
-    """``out[t] = wte[tokens[t]] * scale + wpe[positions[t]]`` (``wpe`` may be None)."""
+    """``out[t] = wte[tokens[t]] * scale + wpe[positions[t]]`` (``wpe`` may be None).  ``out`` has the tables'
+    dtype, or is float32 over bfloat16 tables (a residual stream kept in float32)."""
     _need(tokens, torch.int32, "embed_pos tokens")
-    _need(wte, out.dtype, "embed_pos wte")
+    out_f32 = int(out.dtype == torch.float32 and wte.dtype == torch.bfloat16)
+    if not out_f32:
+        _need(wte, out.dtype, "embed_pos wte")
     T, D = out.shape
     if wte.shape[1] != D or not wte.is_contiguous() or not out.is_contiguous():
         raise KernelError(f"embed_pos: table {tuple(wte.shape)} against output {tuple(out.shape)}")
     if wpe is not None:
         _need(positions, torch.int32, "embed_pos positions")
-        _need(wpe, out.dtype, "embed_pos wpe")
+        _need(wpe, wte.dtype, "embed_pos wpe")
         if wpe.shape[1] != D or not wpe.is_contiguous():
             raise KernelError(f"embed_pos: position table {tuple(wpe.shape)} against width {D}")
-    _call("embed", "mlxb_embed_pos", _EMBED_ARGS, dtype_code(out.dtype), _p(tokens), _p(positions), _p(wte),
-          _p(wpe), _p(out), T, D, wte.shape[0], 0 if wpe is None else wpe.shape[0], scale, _p(status), stream)
+    _call("embed", "mlxb_embed_pos", _EMBED_ARGS, dtype_code(wte.dtype), _p(tokens), _p(positions), _p(wte),
+          _p(wpe), _p(out), T, D, wte.shape[0], 0 if wpe is None else wpe.shape[0], scale, _p(status), stream, out_f32)
 
 
 def gather_tokens(src, index, dst, status, stream) -> None:
@@ -268,8 +271,8 @@ _SIMT_ARGS = [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_
 def linear_generic(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=None) -> None:
     """``out = epilogue(x @ w.T + bias) + residual`` on the CUDA cores in float32 arithmetic.
 
-    ``x [M,K]``, ``w [N,K]`` (rows are output features) and ``residual [M,N]`` share a dtype;
-    ``out [M,N]`` has that dtype or float32; ``bias`` is float32."""
+    ``x [M,K]`` and ``w [N,K]`` (rows are output features) share a dtype; ``out [M,N]`` has that dtype or
+    float32, and ``residual [M,N]`` has the dtype of ``out``; ``bias`` is float32."""
     _need(x, None, "linear x")
     _need(w, x.dtype, "linear w")
     M, K = x.shape
@@ -287,7 +290,7 @@ def linear_generic(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=N
         if bias.numel() != N:
             raise KernelError(f"linear: bias of {bias.numel()} for {N} outputs")
     if residual is not None:
-        _need(residual, x.dtype, "linear residual")
+        _need(residual, out.dtype, "linear residual")
         if residual.shape != out.shape or _rows(residual, "linear residual") != ldc:
             raise KernelError("linear: residual must have the output's shape and row stride")
     _call("gemm_simt", "mlxb_linear_simt", _SIMT_ARGS, dtype_code(x.dtype), out_f32, _p(x), _p(w), _p(bias),
@@ -333,7 +336,7 @@ def linear_few_rows(x, w, bias, out, stream, epilogue: int = EPI_NONE, residual=
         if bias.numel() != N:
             raise KernelError(f"linear: bias of {bias.numel()} for {N} outputs")
     if residual is not None:
-        _need(residual, torch.bfloat16, "linear residual")
+        _need(residual, out.dtype, "linear residual")
         if residual.shape != out.shape or _rows(residual, "linear residual") != ldc:
             raise KernelError("linear: residual must have the output's shape and row stride")
     if fold is not None:
@@ -373,7 +376,7 @@ def linear_tensor_cores(x, w, bias, out, status, stream, epilogue: int = EPI_NON
         if bias.numel() != N:
             raise KernelError(f"linear: bias of {bias.numel()} for {N} outputs")
     if residual is not None:
-        _need(residual, torch.bfloat16, "linear residual")
+        _need(residual, out.dtype, "linear residual")
         if residual.shape != out.shape or _rows(residual, "linear residual") != ldc:
             raise KernelError("linear: residual must have the output's shape and row stride")
     if fold is not None:
@@ -465,7 +468,18 @@ def kv_write(k_src, v_src, positions, token_req, block_table, k_pool, v_pool, st
 
 
 _ATTN_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-              c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p]
+              c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+
+
+def _sinks(sinks, n_heads: int, what: str):
+    """``sinks``: float32 ``[n_heads]`` or None.  A head's sink is one more term ``exp(sink)`` in the denominator
+    of its softmax: it has no key (it is not scaled) and no value."""
+    if sinks is None:
+        return None
+    _need(sinks, torch.float32, what + " sinks")
+    if sinks.numel() != n_heads or not sinks.is_contiguous():
+        raise KernelError(f"{what}: {sinks.numel()} sinks for {n_heads} heads")
+    return sinks.data_ptr()
 
 
 def _attn_shapes(q, out, k_pool, n_heads, what):
@@ -478,7 +492,7 @@ def _attn_shapes(q, out, k_pool, n_heads, what):
 
 
 def attention_generic(q, positions, token_req, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
-                      window: int, status, stream, rows=None) -> None:
+                      window: int, status, stream, rows=None, sinks=None) -> None:
     """Causal attention of tokens over their requests' pages (float32 math, one warp per token and head).
 
     ``q``: ``[T, n_heads*Dh]`` view; ``out``: ``[T, n_heads*Dh]``; ``rows``: int32 token indices to run
@@ -488,25 +502,26 @@ def attention_generic(q, positions, token_req, block_table, k_pool, v_pool, out,
     _call("attention", "mlxb_attention_generic", _ATTN_ARGS, dtype_code(k_pool.dtype), _p(q), _rows(q, "attention q"),
           _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh,
           window, scale, _p(k_pool), _p(v_pool), _p(out), _rows(out, "attention out"), _p(rows), n, _p(status),
-          stream)
+          stream, _sinks(sinks, n_heads, "attention"))
 
 
 _PRE_ARGS = [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
 
 PREFILL_TILE = int(_os.environ.get("MLXB_PREFILL_TILE", "128"))   # queries per CTA of the attention kernels for portions
 PREFILL_TC = _os.environ.get("MLXB_PREFILL_TC", "1") != "0"         # heads of 64 in tiles of 128 on the tcgen05 kernel
 
 _PRE_TC_ARGS = [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+                c_float, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
 
 
-def attention_portions_supported(dtype, head_dim: int) -> bool:
-    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
+def attention_portions_supported(dtype, head_dim: int, scale: float = 1.0) -> bool:
+    # the tensor-core kernels take the maximum of the raw scores before they scale it: the scale must be positive
+    return dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128 and scale > 0
 
 
 def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
-                       window: int, status, stream, tile_rows: int = 0) -> None:
+                       window: int, status, stream, tile_rows: int = 0, sinks=None) -> None:
     """Causal attention of prompt portions on tensor cores (bfloat16, csrc/attention_prefill.cu).
 
     ``tiles``: int32 device tensor ``[n_tiles, 4]``: first token row of the tile, queries in it (1..64),
@@ -521,15 +536,16 @@ def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out,
             and ldq % 8 == 0 and ldo % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
         _call("attention_prefill_tc", "mlxb_attention_prefill_tc", _PRE_TC_ARGS, _p(q), ldq, q.shape[0], _p(tiles),
               n_tiles, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale,
-              _p(k_pool), _p(v_pool), _p(out), ldo, _p(status), stream)
+              _p(k_pool), _p(v_pool), _p(out), ldo, _p(status), stream, _sinks(sinks, n_heads, "attention_portions"))
         return
     _call("attention_prefill", "mlxb_attention_prefill", _PRE_ARGS, _p(q), _rows(q, "attention q"), _p(tiles), n_tiles,
           tile_rows, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
-          _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream)
+          _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream,
+          _sinks(sinks, n_heads, "attention_portions"))
 
 
 _ROWS_ARGS = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p]
+              c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
 
 
 # (row, head) pairs from which single-token rows run on the tensor-core kernel: about seven times the number
@@ -538,10 +554,10 @@ _ROWS_ARGS = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c
 ROWS_MIN_PAIRS = int(_os.environ.get("MLXB_ROWS_MIN_PAIRS", "1024"))
 
 
-def attention_rows_supported(dtype, head_dim: int, n_rows: int = 1 << 30, n_heads: int = 1) -> bool:
+def attention_rows_supported(dtype, head_dim: int, n_rows: int = 1 << 30, n_heads: int = 1, scale: float = 1.0) -> bool:
     """Whether these single-token rows run on the tensor-core kernel (else: ``attention_decode``)."""
     return (dtype == torch.bfloat16 and head_dim % 16 == 0 and 16 <= head_dim <= 128
-            and n_rows * n_heads >= ROWS_MIN_PAIRS)
+            and n_rows * n_heads >= ROWS_MIN_PAIRS and scale > 0)
 
 
 _sm_count = None
@@ -555,7 +571,7 @@ def sm_count() -> int:
 
 
 def attention_rows(q, tiles, n_rows: int, block_table, k_pool, v_pool, out, n_heads: int, scale: float, window: int,
-                   status, stream) -> None:
+                   status, stream, sinks=None) -> None:
     """Attention of rows with a single query each (decode steps) on tensor cores (bfloat16,
     csrc/attention_prefill.cu): ``tiles`` is an int32 device tensor ``[n_rows, 4]`` = (token row, 1, block-table
     row, position), or (token row, 0, 0, 0) for a padding row."""
@@ -565,12 +581,12 @@ def attention_rows(q, tiles, n_rows: int, block_table, k_pool, v_pool, out, n_he
         raise KernelError(f"attention_rows: {tiles.numel()} integers for {n_rows} rows")
     _call("attention_prefill", "mlxb_attention_rows", _ROWS_ARGS, _p(q), _rows(q, "attention q"), _p(tiles), n_rows,
           _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
-          _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream)
+          _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream, _sinks(sinks, n_heads, "attention_rows"))
 
 
 _DEC_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
              c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p,
-             c_void_p]
+             c_void_p, c_void_p]
 
 DECODE_CHUNK = 1024   # key positions per CTA of the single-token attention kernel: a constant, never a function of the batch
 
@@ -582,7 +598,7 @@ def attention_decode_scratch(n_rows: int, n_heads: int, head_dim: int, max_len: 
 
 def attention_decode(q, positions, token_req, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
                      window: int, scratch, counters, max_len: int, status, stream, rows=None,
-                     chunk: int = DECODE_CHUNK) -> None:
+                     chunk: int = DECODE_CHUNK, sinks=None) -> None:
     """Attention for rows with a single query each (decode steps): keys are cut into chunks of ``chunk``
     positions, one CTA per (chunk, head, row) writes a partial result to ``scratch`` (float32, at least
     ``attention_decode_scratch(...)`` elements) and the CTA that finishes last for a (row, head) combines
@@ -598,7 +614,7 @@ def attention_decode(q, positions, token_req, block_table, k_pool, v_pool, out, 
     _call("attention", "mlxb_attention_decode", _DEC_ARGS, dtype_code(k_pool.dtype), _p(q), _rows(q, "attention q"),
           _p(rows), _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv,
           Dh, window, scale, _p(k_pool), _p(v_pool), _p(scratch), _p(counters), n_chunks, chunk, _p(out),
-          _rows(out, "attention out"), n, _p(status), stream)
+          _rows(out, "attention out"), n, _p(status), stream, _sinks(sinks, n_heads, "attention_decode"))
 
 
 # --------------------------------------------------------------------------
@@ -675,3 +691,225 @@ def process_logits(logits, params, context, bias_index, bias_value, stream) -> N
         _need(bias_value, torch.float32, "process_logits bias_value")
     _call("sampling", "mlxb_process_logits", _PROCESS_ARGS, _p(logits), _rows(logits, "process_logits logits"), R, V,
           _p(params), _p(context), C, _p(bias_index) if B else None, _p(bias_value) if B else None, B, stream)
+
+
+# --------------------------------------------------------------------------
+# root-mean-square norms and a float32 residual stream (csrc/rms.cu)
+
+_RMS_ARGS = [c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_float, c_int, c_void_p, c_int, c_int, c_void_p, c_int,
+             c_int, c_int, c_int, c_float, c_void_p]
+
+GATE_NONE, GATE_BEFORE, GATE_AFTER = 0, 1, 2
+
+
+def rmsnorm(x, weight, out, eps: float, stream, offset: float = 0.0, groups: int = 1, period: Optional[int] = None,
+            gate=None, gate_mode: int = GATE_NONE, rows=None) -> None:
+    """``out[r] = x[r] / sqrt(mean(x[r]^2) + eps) * (offset + weight)`` over float32 rows, the row cut into
+    ``groups`` equal parts that are normed each by itself; ``weight`` (float32) repeats every ``period`` columns
+    (default: the width).  ``gate`` (``out``'s dtype, the shape of ``x``): ``GATE_BEFORE`` multiplies ``x`` by
+    ``silu(gate)`` before the statistics, ``GATE_AFTER`` multiplies the normed value.  ``rows``: int32 indices of
+    the input rows to take."""
+    _need(x, torch.float32, "rmsnorm x")
+    _need(weight, torch.float32, "rmsnorm weight")
+    R, D = out.shape
+    period = D if period is None else int(period)
+    if x.shape[1] != D or weight.numel() != period or D % groups:
+        raise KernelError(f"rmsnorm: x {tuple(x.shape)}, weight of {weight.numel()} every {period}, {groups} parts, "
+                          f"out {tuple(out.shape)}")
+    if rows is not None:
+        _need(rows, torch.int32, "rmsnorm rows")
+        if rows.numel() != R:
+            raise KernelError(f"rmsnorm: {rows.numel()} row indices for {R} output rows")
+    elif x.shape[0] != R:
+        raise KernelError(f"rmsnorm: {x.shape[0]} input rows for {R} output rows")
+    ldg = 0
+    if gate is not None:
+        _need(gate, out.dtype, "rmsnorm gate")
+        if gate.shape != x.shape or gate_mode not in (GATE_BEFORE, GATE_AFTER):
+            raise KernelError(f"rmsnorm: gate {tuple(gate.shape)} in mode {gate_mode} for x {tuple(x.shape)}")
+        ldg = _rows(gate, "rmsnorm gate")
+    elif gate_mode != GATE_NONE:
+        raise KernelError("rmsnorm: a gate mode without a gate")
+    _call("rms", "mlxb_rmsnorm", _RMS_ARGS, dtype_code(out.dtype), _p(x), _rows(x, "rmsnorm x"), _p(rows), x.shape[0],
+          _p(weight), float(offset), period, _p(gate), ldg, gate_mode, _p(out), _rows(out, "rmsnorm out"), R, D,
+          groups, float(eps), stream)
+
+
+_RESUP_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_float, c_float, c_void_p, c_int,
+               c_int, c_int, c_void_p]
+
+
+def residual_update(x, y1, stream, w1=None, y2=None, w2=None, scale: float = 1.0, eps: float = 0.0, cast_out=None) -> None:
+    """``x += scale * (f1(y1) + f2(y2))`` in place on float32 rows; ``f_i`` is the RMS norm over the whole row
+    with the plain weight ``w_i`` (float32), or the identity where ``w_i`` is None.  ``cast_out``: a copy of the
+    new rows in its own dtype."""
+    _need(x, torch.float32, "residual_update x")
+    _need(y1, torch.float32, "residual_update y1")
+    R, D = x.shape
+    if y1.shape != x.shape or (y2 is not None and (y2.shape != x.shape or y2.dtype != torch.float32)):
+        raise KernelError(f"residual_update: x {tuple(x.shape)}, y1 {tuple(y1.shape)}")
+    ldy = _rows(y1, "residual_update y1")
+    if y2 is not None and _rows(y2, "residual_update y2") != ldy:
+        raise KernelError("residual_update: the two inputs must share a row stride")
+    for w in (w1, w2):
+        if w is not None:
+            _need(w, torch.float32, "residual_update weight")
+            if w.numel() != D:
+                raise KernelError(f"residual_update: weight of {w.numel()} for width {D}")
+    ldc, code = 0, F32
+    if cast_out is not None:
+        if cast_out.shape != x.shape:
+            raise KernelError("residual_update: cast_out must have the shape of x")
+        ldc, code = _rows(cast_out, "residual_update cast_out"), dtype_code(cast_out.dtype)
+    _call("rms", "mlxb_residual_update", _RESUP_ARGS, code, _p(x), _rows(x, "residual_update x"), _p(y1), _p(w1), _p(y2),
+          _p(w2), ldy, float(scale), float(eps), _p(cast_out), ldc, R, D, stream)
+
+
+# --------------------------------------------------------------------------
+# layers with a state of fixed size per request (csrc/recurrent.cu)
+
+_CONV_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+              c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
+
+
+def conv_silu(x, weight, bias, state, slots, positions, token_req, req_first_token, req_first_position, out,
+              stream) -> None:
+    """Causal convolution over time per channel, then silu: ``out[t, c] = silu(bias[c] + sum_j weight[c, taps-1-j]
+    * x(t - j, c))``.  ``x``: ``[T, C]`` view (contiguous rows); ``weight`` float32 ``[C, taps]`` (last column: the
+    current token); ``state`` float32 ``[slots, taps-1, C]``: each request's last inputs, read for the rows that
+    reach back before the step and brought up to date afterwards (two launches)."""
+    _need(x, out.dtype, "conv x")
+    _need(weight, torch.float32, "conv weight")
+    _need(state, torch.float32, "conv state")
+    T, C = out.shape
+    taps = weight.shape[1]
+    if x.shape != out.shape or weight.shape[0] != C or state.shape[1:] != (taps - 1, C) or not state.is_contiguous() \
+            or not weight.is_contiguous():
+        raise KernelError(f"conv: x {tuple(x.shape)}, weight {tuple(weight.shape)}, state {tuple(state.shape)}, "
+                          f"out {tuple(out.shape)}")
+    if bias is not None:
+        _need(bias, torch.float32, "conv bias")
+    _call("recurrent", "mlxb_conv_silu", _CONV_ARGS, dtype_code(out.dtype), _p(x), _rows(x, "conv x"), _p(weight),
+          _p(bias), taps, C, _p(state), _p(slots), _p(positions), _p(token_req), _p(req_first_token),
+          _p(req_first_position), _p(out), _rows(out, "conv out"), T, slots.numel(), stream)
+
+
+_M2_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+
+
+def mamba2_scan(xbc, x_off: int, b_off: int, c_off: int, dt_raw, dt_bias, a_log, d_skip, state, slots, token_req,
+                req_first_token, y, n_heads: int, n_groups: int, stream) -> None:
+    """The selective state-space recurrence per (request, head): ``S <- exp(-exp(A_log) dt) S + dt B x^T``,
+    ``y = S^T C + D x`` with ``dt = softplus(dt_raw + dt_bias)``.  ``xbc [T, .]`` holds x, B, C from the given
+    column offsets; ``state`` float32 ``[slots, heads, N, V]``; ``y`` float32 ``[T, heads*V]``."""
+    _need(xbc, dt_raw.dtype, "mamba2_scan xbc")
+    _need(state, torch.float32, "mamba2_scan state")
+    _need(y, torch.float32, "mamba2_scan y")
+    _, H, N, V = state.shape
+    if H != n_heads or y.shape[1] != H * V or not state.is_contiguous():
+        raise KernelError(f"mamba2_scan: state {tuple(state.shape)} for {n_heads} heads, y {tuple(y.shape)}")
+    for t in (dt_bias, a_log, d_skip):
+        _need(t, torch.float32, "mamba2_scan head constants")
+    _call("recurrent", "mlxb_mamba2_scan", _M2_ARGS, dtype_code(xbc.dtype), _p(xbc), _rows(xbc, "mamba2_scan xbc"), x_off,
+          b_off, c_off, _p(dt_raw), _rows(dt_raw, "mamba2_scan dt"), _p(dt_bias), _p(a_log), _p(d_skip), _p(state),
+          _p(slots), _p(token_req), _p(req_first_token), _p(y), _rows(y, "mamba2_scan y"), H, n_groups, N, V,
+          slots.numel(), stream)
+
+
+_GD_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
+            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+
+
+def gated_delta_scan(qkv, q_off: int, k_off: int, v_off: int, b_raw, a_raw, dt_bias, a_log, state, slots, token_req,
+                     req_first_token, o, n_heads: int, n_key_heads: int, stream) -> None:
+    """The gated delta rule per (request, head): ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` with
+    q and k made unit vectors (q also divided by sqrt(dim)), ``beta = sigmoid(b_raw)``,
+    ``g = exp(-exp(A_log) softplus(a_raw + dt_bias))``.  ``state`` float32 ``[slots, heads, K, V]``; ``o`` float32."""
+    _need(state, torch.float32, "gated_delta_scan state")
+    _need(o, torch.float32, "gated_delta_scan o")
+    _need(b_raw, qkv.dtype, "gated_delta_scan b")
+    _need(a_raw, qkv.dtype, "gated_delta_scan a")
+    _, H, K, V = state.shape
+    if H != n_heads or o.shape[1] != H * V or not state.is_contiguous():
+        raise KernelError(f"gated_delta_scan: state {tuple(state.shape)} for {n_heads} heads, o {tuple(o.shape)}")
+    _call("recurrent", "mlxb_gated_delta_scan", _GD_ARGS, dtype_code(qkv.dtype), _p(qkv), _rows(qkv, "gated_delta qkv"),
+          q_off, k_off, v_off, _p(b_raw), _rows(b_raw, "gated_delta b"), _p(a_raw), _rows(a_raw, "gated_delta a"),
+          _p(dt_bias), _p(a_log), _p(state), _p(slots), _p(token_req), _p(req_first_token), _p(o),
+          _rows(o, "gated_delta o"), H, n_key_heads, K, V, slots.numel(), stream)
+
+
+# --------------------------------------------------------------------------
+# queries, keys and values into shape for the attention kernels (csrc/rotary.cu)
+
+_QKVP_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+              c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
+              c_void_p, c_int, c_int, c_void_p, c_void_p]
+
+
+def qkv_prepare(proj, q_off: int, k_off: int, v_off: int, n_heads: int, n_kv_heads: int, dk: int, dv: int, q_norm,
+                k_norm, eps: float, freq, positions, token_req, block_table, k_pool, v_pool, q_out, write: bool, status,
+                stream) -> None:
+    """From a fused projection ``proj [T, .]``: optional RMS norm over a token's whole q and whole k projection
+    (float32 weights ``q_norm``, ``k_norm`` or None), rotation of the first ``2 * len(freq)`` dimensions of every
+    head by the token's position (pairs ``(i, i + len(freq))``; ``freq`` float32 or None), q into ``q_out
+    [T, n_heads*Dh]``, k and v into the pages ``[n_pages, n_kv_heads, page, Dh]``; columns of a head beyond
+    ``dk`` / ``dv`` are zeros."""
+    n_pages, Hkv, page, Dh = k_pool.shape
+    _need(proj, k_pool.dtype, "qkv_prepare proj")
+    _need(q_out, k_pool.dtype, "qkv_prepare q_out")
+    if Hkv != n_kv_heads or q_out.shape[1] != n_heads * Dh or not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+        raise KernelError(f"qkv_prepare: pools {tuple(k_pool.shape)}, q_out {tuple(q_out.shape)}")
+    half = 0
+    if freq is not None:
+        _need(freq, torch.float32, "qkv_prepare freq")
+        half = freq.numel()
+    for w, n in ((q_norm, n_heads * dk), (k_norm, n_kv_heads * dk)):
+        if w is not None:
+            _need(w, torch.float32, "qkv_prepare norm weight")
+            if w.numel() != n:
+                raise KernelError(f"qkv_prepare: norm weight of {w.numel()} for {n} columns")
+    _call("rotary", "mlxb_qkv_prepare", _QKVP_ARGS, dtype_code(k_pool.dtype), _p(proj), _rows(proj, "qkv_prepare proj"),
+          q_off, k_off, v_off, n_heads, n_kv_heads, dk, dv, Dh, _p(q_norm), _p(k_norm), float(eps), _p(freq), half,
+          _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, _p(q_out),
+          _rows(q_out, "qkv_prepare q_out"), _p(k_pool), _p(v_pool), int(bool(write)), proj.shape[0], _p(status), stream)
+
+
+# --------------------------------------------------------------------------
+# small row-wise kernels (csrc/elementwise.cu)
+
+def gated_unit(x, out, stream) -> None:
+    """``out[t, j] = silu(x[t, j]) * x[t, F + j]`` for ``x [T, 2F]``: the halves of a fused [gate | up] projection."""
+    _need(x, out.dtype, "gated_unit x")
+    T, F_ = out.shape
+    if x.shape != (T, 2 * F_):
+        raise KernelError(f"gated_unit: x {tuple(x.shape)} for out {tuple(out.shape)}")
+    _call("elementwise", "mlxb_gated_unit", [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+          dtype_code(out.dtype), _p(x), _rows(x, "gated_unit x"), _p(out), _rows(out, "gated_unit out"), F_, T, stream)
+
+
+def scale_by_rows(x, index, table, first: int, out, status, stream) -> None:
+    """``out[t, j] = x[t, j] * table[index[t], first + j]``."""
+    _need(x, out.dtype, "scale_by_rows x")
+    _need(table, out.dtype, "scale_by_rows table")
+    _need(index, torch.int32, "scale_by_rows index")
+    T, F_ = out.shape
+    if x.shape != out.shape or table.dim() != 2:
+        raise KernelError(f"scale_by_rows: x {tuple(x.shape)}, out {tuple(out.shape)}, table {tuple(table.shape)}")
+    _call("elementwise", "mlxb_scale_by_rows",
+          [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+           c_void_p],
+          dtype_code(out.dtype), _p(x), _rows(x, "scale_by_rows x"), _p(index), _p(table), _rows(table, "table"),
+          table.shape[0], first, _p(out), _rows(out, "scale_by_rows out"), F_, T, _p(status), stream)
+
+
+def join_rows(a, b, out, stream) -> None:
+    """``out[t] = [a[t] | b[t]]`` in ``out``'s dtype from contiguous float32 rows (``b`` None: a cast of ``a``)."""
+    _need(a, torch.float32, "join_rows a")
+    T, D = a.shape
+    if not a.is_contiguous() or (b is not None and (b.shape != a.shape or b.dtype != torch.float32 or not b.is_contiguous())):
+        raise KernelError(f"join_rows: a {tuple(a.shape)}")
+    if out.shape != (T, D * (2 if b is not None else 1)):
+        raise KernelError(f"join_rows: out {tuple(out.shape)} for rows of {D}")
+    _call("elementwise", "mlxb_join_rows", [c_int, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p],
+          dtype_code(out.dtype), _p(a), _p(b), D, _p(out), _rows(out, "join_rows out"), T, stream)

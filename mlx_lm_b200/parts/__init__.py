@@ -1,14 +1,18 @@
 from .base import (INT_TABLE, MATRIX, VECTOR, Block, FeedForward, Init, Mixer, Norm, PagedKVSpec, ParamSpec, Part,
                    PositionEncoding, StateSpec, make_part, register_part, registered_parts)
-from .block import PreNormBlock
-from .feed_forward import MLP
-from .linear import Linear
-from .mixers import Attention
-from .model import Model, ModelDescription, OutputHead, RunEntry, TokenEmbedding
-from .norms import LayerNorm
+from .block import PreNormBlock, StreamBlock
+from .feed_forward import MLP, GatedMLP
+from .linear import FusedLinear, Linear
+from .mixers import Attention, ParallelMixer, SinkAttention
+from .model import LoopInput, Model, ModelDescription, OutputHead, Reentry, RunEntry, TokenEmbedding
+from .norms import LayerNorm, RMSNorm
+from .recurrent import GatedDeltaMixer, Mamba2Mixer
+from .side import TokenSideInput
 from .positions import LearnedAbsolute, NoPosition
 
 __all__ = ["INT_TABLE", "MATRIX", "VECTOR", "Block", "FeedForward", "Init", "Mixer", "Norm", "PagedKVSpec",
            "ParamSpec", "Part", "PositionEncoding", "StateSpec", "make_part", "register_part", "registered_parts",
            "PreNormBlock", "MLP", "Linear", "Attention", "Model", "ModelDescription", "OutputHead", "RunEntry",
-           "TokenEmbedding", "LayerNorm", "LearnedAbsolute", "NoPosition"]
+           "TokenEmbedding", "LayerNorm", "LearnedAbsolute", "NoPosition", "StreamBlock", "GatedMLP", "FusedLinear",
+           "ParallelMixer", "SinkAttention", "LoopInput", "Reentry", "RMSNorm", "GatedDeltaMixer", "Mamba2Mixer",
+           "TokenSideInput"]

@@ -6,6 +6,7 @@ the epilogues of the mixer's and the feed-forward's last products."""
 from __future__ import annotations
 
 import os
+from typing import Optional
 
 import torch
 
@@ -42,4 +43,34 @@ class PreNormBlock(Block):
         return self.feed_forward.forward(ctx, n2, h)
 
 
+class StreamBlock(Block):
+    """A pre-norm block over a float32 residual stream: ``x += mixer(norm_1(x))``, then, if the layer has a
+    feed-forward, ``x += feed_forward(norm_2(x))``, then any number of further branches, each of which reads the
+    stream and adds to it (``branch.forward(ctx, x) -> x``).  Norms give the run's dtype to the products; the sums
+    stay float32 whatever the run's dtype is."""
+    replayable = True
+
+    def __init__(self, norm_1: Norm, mixer: Mixer, norm_2: Optional[Norm] = None,
+                 feed_forward: Optional[FeedForward] = None, branches=()):
+        if (norm_2 is None) != (feed_forward is None):
+            raise ValueError("a feed-forward and the norm before it come together")
+        self.norm_1, self.mixer, self.norm_2, self.feed_forward = norm_1, mixer, norm_2, feed_forward
+        self.branches = tuple(branches)
+
+    def children(self):
+        return tuple(p for p in (self.norm_1, self.mixer, self.norm_2, self.feed_forward) if p is not None) + self.branches
+
+    def cache_spec(self):
+        return self.mixer.cache_spec()
+
+    def forward(self, ctx, x, cache):
+        x = self.mixer.forward(ctx, self.norm_1.forward(ctx, x), x, cache)
+        if self.feed_forward is not None:
+            x = self.feed_forward.forward(ctx, self.norm_2.forward(ctx, x), x)
+        for b in self.branches:
+            x = b.forward(ctx, x)
+        return x
+
+
 register_part("block", "pre_norm", PreNormBlock)
+register_part("block", "stream", StreamBlock)

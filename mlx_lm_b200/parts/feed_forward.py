@@ -6,7 +6,10 @@ epilogue and the residual add in the second's."""
 from __future__ import annotations
 
 from .base import FeedForward, Init, register_part
-from .linear import ACTIVATIONS, Linear
+import torch
+
+from .. import ops
+from .linear import ACTIVATIONS, FusedLinear, Linear
 
 
 class MLP(FeedForward):
@@ -33,3 +36,32 @@ class MLP(FeedForward):
 
 
 register_part("feed_forward", "mlp", MLP)
+
+
+class GatedMLP(FeedForward):
+    """``down(silu(gate(x)) * up(x))`` without biases.  ``gate`` and ``up`` run as one product whose two halves
+    a small kernel multiplies; the residual stream (float32) is added in the last product's epilogue."""
+    replayable = True
+    kernel_libs = ("elementwise",)
+
+    def __init__(self, name: str, width: int, inner: int, gate_name: str = "gate", up_name: str = "up",
+                 down_name: str = "down", init: Init = Init()):
+        self.name, self.width, self.inner = name, width, inner
+        self.gate_up = FusedLinear(f"{name}.gate_up", width, [(f"{name}.{gate_name}", inner), (f"{name}.{up_name}", inner)],
+                                   init=init)
+        self.down = Linear(f"{name}.{down_name}", inner, width, bias=False, weight_suffix="", init=init)
+
+    def children(self):
+        return (self.gate_up, self.down)
+
+    def forward(self, ctx, x, residual):
+        T = x.shape[0]
+        both = ctx.ws.get("ffn_gate_up", T, 2 * self.inner, x.dtype)
+        self.gate_up.forward(ctx, x, both)
+        h = ctx.ws.get("ffn_hidden", T, self.inner, x.dtype)
+        ops.label(self.name + ".act", 4.0 * T * self.inner, 3.0 * x.element_size() * T * self.inner)
+        ops.gated_unit(both, h, ctx.stream)
+        return self.down.forward(ctx, h, residual, residual=residual)
+
+
+register_part("feed_forward", "gated_mlp", GatedMLP)

@@ -131,3 +131,29 @@ class Linear(Part):
         else:
             ops.linear_generic(x, self.weight, self.bias, out, ctx.stream, epilogue=epi, residual=residual)
         return out
+
+
+class FusedLinear(Linear):
+    """Several linear layers that read the same input, stored as separate ``[out, in]`` tensors and run as one
+    product: the weights are stacked at bind time, the output holds the layers' results side by side in the
+    order of ``sources`` (``offset(name)`` gives a layer's first column).  No biases."""
+
+    def __init__(self, name: str, n_in: int, sources, init: Init = Init(), tensor_core_from: Optional[int] = None):
+        self.sources = [(str(n), int(k)) for n, k in sources]
+        super().__init__(name, n_in, sum(k for _, k in self.sources), bias=False, stored="out_in", weight_suffix="",
+                         init=init, tensor_core_from=tensor_core_from)
+
+    def offset(self, tensor_name: str) -> int:
+        off = 0
+        for n, k in self.sources:
+            if n == tensor_name:
+                return off
+            off += k
+        raise KeyError(tensor_name)
+
+    def param_specs(self) -> List[ParamSpec]:
+        return [ParamSpec(n, (k, self.n_in), MATRIX, self.init) for n, k in self.sources]
+
+    def bind(self, tensors, dtype, device) -> None:
+        self.weight = torch.cat([tensors[n] for n, _ in self.sources], dim=0).contiguous()
+        self.bias = None

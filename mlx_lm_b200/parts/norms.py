@@ -4,7 +4,7 @@ call sites in mlx_lm/models/gpt2.py:92-96, 123."""
 
 from __future__ import annotations
 
-from typing import List
+from typing import List, Optional
 
 from .. import ops
 from .base import VECTOR, Init, Norm, ParamSpec, register_part
@@ -41,4 +41,32 @@ class LayerNorm(Norm):
         return out
 
 
+class RMSNorm(Norm):
+    """``x / sqrt(mean(x^2) + eps) * (offset + weight)`` over float32 rows, result in the run's dtype.
+    ``offset = 1``: the weight is stored as its distance from one; ``offset = 0``: as it is."""
+    replayable = True
+    kernel_libs = ("rms",)
+
+    def __init__(self, name: str, width: int, eps: float, offset: float = 0.0, weight_suffix: str = "",
+                 init: Optional[Init] = None):
+        self.name, self.width, self.eps, self.offset = name, width, float(eps), float(offset)
+        self.weight_name = name + weight_suffix
+        self.init = init if init is not None else Init(1.0 - self.offset, 0.1)
+        self.weight = None
+
+    def param_specs(self) -> List[ParamSpec]:
+        return [ParamSpec(self.weight_name, (self.width,), VECTOR, self.init)]
+
+    def bind(self, tensors, dtype, device) -> None:
+        self.weight = tensors[self.weight_name]
+
+    def forward(self, ctx, x, rows=None, tag: str = "normed"):
+        n = x.shape[0] if rows is None else rows.numel()
+        out = ctx.ws.get(tag, n, self.width, ctx.dtype)
+        ops.label(self.name, 4.0 * n * self.width, (4.0 + out.element_size()) * n * self.width)
+        ops.rmsnorm(x, self.weight, out, self.eps, ctx.stream, offset=self.offset, rows=rows)
+        return out
+
+
 register_part("norm", "layer_norm", LayerNorm)
+register_part("norm", "rms_norm", RMSNorm)

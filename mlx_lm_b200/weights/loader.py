@@ -131,6 +131,7 @@ def load_model(model_path: str, dtype="bfloat16", device="cuda", model_config: O
     if model_config:
         config.update(model_config)
     model = build_model(config, read_safetensors(model_path), parse_dtype(dtype), device, get_model_classes)
+    config.setdefault("vocab_size", model.vocab_size)     # callers size their tokens by it, whatever the config calls it
     return model, config
 
 
