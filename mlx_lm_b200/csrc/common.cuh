@@ -86,6 +86,11 @@ static inline bool mlxb_pdl_enabled() {
   if (on < 0) {
     const char* e = getenv("MLXB_PDL");
     on = (e && e[0] == '0') ? 0 : 1;
+#ifdef MLXB_LIB_NAME
+    // MLXB_PDL_OFF=name,name: the libraries (kernel source files) whose launches do without the attribute
+    const char* off = getenv("MLXB_PDL_OFF");
+    if (on && off && strstr(off, MLXB_LIB_NAME)) on = 0;
+#endif
   }
   return on == 1;
 }

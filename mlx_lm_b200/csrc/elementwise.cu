@@ -11,8 +11,8 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); 
 
 template <typename T>
 __global__ void gated_unit_kernel(const T* in, int ldi, T* __restrict__ out, int ldo, int F, int n) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   in = after_wait(in);
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)n * F) return;
@@ -42,8 +42,8 @@ template <typename T>
 __global__ void scale_by_rows_kernel(const T* in, int ldi, const int* __restrict__ index, const T* __restrict__ table,
                                      int ldt, int n_table_rows, int first, T* __restrict__ out, int ldo, int F, int n,
                                      int* __restrict__ status) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   in = after_wait(in);
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= (long long)n * F) return;
@@ -77,8 +77,8 @@ MLXB_EXPORT int mlxb_scale_by_rows(int dtype, const void* in, int ldi, const int
 
 template <typename T>
 __global__ void join_rows_kernel(const float* a, const float* b, int D, T* __restrict__ out, int ldo, int n) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   a = after_wait(a);
   b = after_wait(b);
   const int W = b ? 2 * D : D;

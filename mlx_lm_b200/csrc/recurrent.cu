@@ -43,13 +43,13 @@ __global__ void conv_silu_kernel(const T* in, int ldi, const float* __restrict__
                                  int taps, int C, const float* state, const int* __restrict__ slots,
                                  const int* __restrict__ positions, const int* __restrict__ token_req,
                                  const int* __restrict__ req_first_position, T* __restrict__ out, int ldo) {
-  pdl_trigger();
   const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
   const int r = token_req[t];
   if (r < 0 || c >= C) return;
   const int i = positions[t] - req_first_position[r];   // rows of this run before t
   const int slot = slots[r];
   pdl_wait();
+  pdl_trigger();
   in = after_wait(in);
   state = after_wait(state);
   float acc = bias ? bias[c] : 0.f;
@@ -66,8 +66,8 @@ template <typename T>
 __global__ void conv_state_update_kernel(const T* in, int ldi, int taps, int C, float* state,
                                          const int* __restrict__ slots, const int* __restrict__ token_req,
                                          const int* __restrict__ req_first_token) {
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   in = after_wait(in);
   const int r = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
   const int t0 = req_first_token[r], t1 = req_first_token[r + 1];
@@ -160,10 +160,10 @@ mamba2_scan_kernel(const T* xbc, int ldx, int x_off, int b_off, int c_off, const
   float* sx = sC + SCAN_CHUNK * N;         // [CHUNK][VB]
   float* sdt = sx + SCAN_CHUNK * VB;       // [CHUNK]
   float* sa = sdt + SCAN_CHUNK;            // [CHUNK]
-  pdl_trigger();
   const int h = blockIdx.x, r = blockIdx.y, vb = blockIdx.z;
   const int t0 = req_first_token[r], t1 = req_first_token[r + 1];
   pdl_wait();
+  pdl_trigger();
   xbc = after_wait(xbc);
   dt_raw = after_wait(dt_raw);
   const int n = request_rows(token_req, t0, t1, r);
@@ -271,10 +271,10 @@ gated_delta_scan_kernel(const T* qkv, int ldq, int q_off, int k_off, int v_off, 
   float* sv = sk + SCAN_CHUNK * K;         // [CHUNK][VB]
   float* sbeta = sv + SCAN_CHUNK * VB;     // [CHUNK]
   float* sg = sbeta + SCAN_CHUNK;          // [CHUNK]
-  pdl_trigger();
   const int h = blockIdx.x, r = blockIdx.y, vb = blockIdx.z;
   const int t0 = req_first_token[r], t1 = req_first_token[r + 1];
   pdl_wait();
+  pdl_trigger();
   qkv = after_wait(qkv);
   b_raw = after_wait(b_raw);
   a_raw = after_wait(a_raw);

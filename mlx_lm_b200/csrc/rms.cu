@@ -21,8 +21,8 @@ __global__ void rmsnorm_kernel(const float* x, int ldx, const int* __restrict__ 
                                const float* __restrict__ w, float offset, int period, const TO* gate, int ldg,
                                int gate_mode, TO* __restrict__ out, int ldo, int D, int groups, float eps) {
   __shared__ float red[33];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   x = after_wait(x);
   gate = after_wait(gate);
   const int r = blockIdx.x, g = blockIdx.y;
@@ -80,8 +80,8 @@ __global__ void residual_update_kernel(float* x, int ldx, const float* y1, const
                                        const float* y2, const float* __restrict__ w2, int ldy, float scale, float eps,
                                        TO* __restrict__ cast_out, int ldc, int D) {
   __shared__ float red[33];
-  pdl_trigger();
   pdl_wait();
+  pdl_trigger();
   x = after_wait(x);
   y1 = after_wait(y1);
   y2 = after_wait(y2);

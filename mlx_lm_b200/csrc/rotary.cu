@@ -22,7 +22,6 @@ __global__ void qkv_prepare_kernel(const T* proj, int ld, int q_off, int k_off, 
                                    T* __restrict__ q_out, int ldq, T* __restrict__ k_pool, T* __restrict__ v_pool,
                                    int write, int* __restrict__ status) {
   __shared__ float red[33];
-  pdl_trigger();
   const int t = blockIdx.x;
   const int r = token_req[t];
   if (r < 0) return;
@@ -42,6 +41,7 @@ __global__ void qkv_prepare_kernel(const T* proj, int ld, int q_off, int k_off, 
     }
   }
   pdl_wait();
+  pdl_trigger();
   proj = after_wait(proj);
   const T* row = proj + (size_t)t * ld;
   float rq = 1.f, rk = 1.f;

@@ -115,7 +115,8 @@ def _compile(name: str) -> str:
     if not os.path.exists(src):
         raise KernelBuildError(f"no kernel source {src}")
     tmp = f"{out}.{os.getpid()}.tmp"
-    cmd = [_nvcc()] + NVCC_FLAGS + ["-D" + d for d in defines] + ["-I", CSRC, "-o", tmp, src, "-lcuda"]
+    cmd = ([_nvcc()] + NVCC_FLAGS + ["-D" + d for d in defines] + [f'-DMLXB_LIB_NAME="{stem}"']
+           + ["-I", CSRC, "-o", tmp, src, "-lcuda"])
     t0 = time.time()
     label = stem + ".cu" + (" with " + ", ".join(defines) if defines else "")
     print(f"[mlx_lm_b200] compiling {label} for sm_100a ...", file=sys.stderr, flush=True)
