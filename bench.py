@@ -322,6 +322,7 @@ def kernel_table(calls, pk, mode, attention_bytes=0.0, attention_flops=0.0, reps
         lab = c[4] or ("?", 0.0, 0.0)
         kind = re.sub(r"\.\d+\.", ".", lab[0])
         kind = re.sub(r"^h\.", "", kind)
+        kind = re.sub(r"^l\d+\.", "", kind)       # layers named l<i>.
         groups.setdefault(kind, []).append(c)
     side = torch.cuda.Stream()
     flush = torch.empty(256 << 20, dtype=torch.uint8, device="cuda")
@@ -377,6 +378,11 @@ def kernel_table(calls, pk, mode, attention_bytes=0.0, attention_flops=0.0, reps
             rec["frac"] = round(nbytes / (us * 1e-6) / 1e9 / pk["hbm_gbs"], 3)
         elif mode == "prefill" and flops:
             rec["frac"] = round(flops / (us * 1e-6) / 1e12 / pk["bf16_tflops"], 3)
+        elif mode == "roofline" and (flops or nbytes):
+            # against whichever bound is the tighter one for this kernel: its bytes at the measured copy
+            # bandwidth or its flops at the measured bf16 peak
+            need_us = max(nbytes / (pk["hbm_gbs"] * 1e3), flops / (pk["bf16_tflops"] * 1e6))
+            rec["frac"] = round(need_us / us, 3)
         out[kind] = rec
     return out
 
@@ -641,6 +647,101 @@ def prefill_step(engine, cfg, pk, vocab, n_pf, lin_flops, table=False):
     return prefill, pf_ms, tab
 
 
+# ---------------------------------------------------------------------------------------------------
+# --only lelatar: the Lelatar design beside GPT-2 at equal width and equal numbers of layer runs
+
+def lelatar_config(width, vocab):
+    """Layers of the sizes a model of this width would have: heads of 64, a state of 128, a feed-forward of about
+    2.7 times the width on every second layer, the first four layers run twice."""
+    H = width // 64
+    mamba = lambda mlp: {"type": "mamba2", "mlp": mlp, "mixer": {"conv": 4, "groups": 1, "heads": 2 * H, "norm_groups": 1,
+                                                                 "state": 128, "vdim": 64}}
+    ff = {"ff": (width * 11 // 4 + 127) // 128 * 128, "kind": "dense"}
+    par = {"type": "parallel", "mlp": ff,
+           "mixer": {"left": {"dim": 64, "heads": H, "kv_heads": max(1, H // 4), "vdim": 64, "scale": 0.125,
+                              "rot": {"base": 500000.0, "dims": 32}},
+                     "right": {"conv": 4, "dim": 64, "heads": H, "kv_heads": max(1, H // 4), "vdim": 64}}}
+    return {"architecture": "Lelatar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "token_side": {"dim": 64},
+            "loop": {"start": 0, "stop": 4, "times": 2}, "layers": [mamba(None), par, mamba(ff), par, mamba(None), par]}
+
+
+def run_lelatar(args):
+    """Prefill (2 x 1024 tokens in one step) and decode (batch 8 and 64 at 512 tokens of context, through
+    Engine.step) of Lelatar models with random weights at two widths, beside GPT-2 models of the same width and
+    as many layer runs, and the kernels of both timed alone against their rooflines."""
+    import torch
+
+    from mlx_lm_b200.engine import Engine, StepEntry
+    from mlx_lm_b200.config import get_architecture
+    from mlx_lm_b200.weights.loader import build_model, random_tensors
+
+    pk = peaks()
+    vocab = 32000
+    out = {"metric": "lelatar_vs_gpt2", "dtype": "bf16", "data": "synthetic", "peaks": pk, "models": []}
+    widths = [int(w) for w in (args.widths.split(",") if args.widths else ["1024", "2048"])]
+    for width in widths:
+        lel = lelatar_config(width, vocab)
+        runs = len(lel["layers"]) + (lel["loop"]["times"] - 1) * (lel["loop"]["stop"] - lel["loop"]["start"])
+        gpt = dict(model_type="gpt2", n_layer=runs, n_embd=width, n_head=width // 64, n_inner=4 * width, vocab_size=vocab,
+                   n_positions=2048, layer_norm_epsilon=1e-5, activation_function="gelu_new")
+        for name, cfg in (("lelatar", lel), ("gpt2", gpt)):
+            arch = get_architecture(cfg)
+            description = arch.build(arch.args_class.from_dict(dict(cfg)))
+            model = build_model(dict(cfg), random_tensors(description, 0), torch.bfloat16, "cuda")
+            n_params = model.n_parameters()
+            engine = Engine(model, page_size=PAGE_SIZE, n_pages=64 * 2048 // PAGE_SIZE, max_requests=64, max_len=2048)
+            g = torch.Generator().manual_seed(1)
+            rec = {"model": name, "width": width, "layer_runs": runs, "parameters": n_params}
+
+            def timed(entries_of, reps, setup=None, finish=None):
+                times = []
+                for it in range(reps):
+                    if setup:
+                        setup()
+                    torch.cuda.synchronize()
+                    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    s.record()
+                    engine.step(entries_of(it))
+                    e.record()
+                    torch.cuda.synchronize()
+                    times.append(s.elapsed_time(e))
+                    if finish:
+                        finish()
+                return times
+
+            # prefill: two whole prompts of 1024 tokens in one step
+            prompts = [torch.randint(0, vocab, (1024,), generator=g).tolist() for _ in range(2)]
+            t = timed(lambda it: [StepEntry(("pf", i), prompts[i], [1023]) for i in range(2)], 5,
+                      setup=lambda: [engine.add_request(("pf", i)) for i in range(2)],
+                      finish=lambda: [engine.finish(("pf", i)) for i in range(2)])
+            ms = min(t[1:])
+            rec["prefill"] = {"tokens": 2048, "ms": round(ms, 3), "tokens_per_s": round(2048 / ms * 1e3, 1)}
+            rec["prefill_kernels"] = kernel_table(engine.last_calls, pk, "roofline",
+                                                  attention_flops=2 * 4 * width * (1024 * 1025 // 2),
+                                                  attention_bytes=2 * 1024 * 4 * width * 2)
+            # decode: every request brings one token, 512 tokens of context
+            for batch in (8, 64):
+                ctx = [torch.randint(0, vocab, (512,), generator=g).tolist() for _ in range(batch)]
+                for i in range(batch):
+                    engine.add_request(("d", i))
+                for i0 in range(0, batch, 8):
+                    engine.step([StepEntry(("d", i), ctx[i], []) for i in range(i0, min(batch, i0 + 8))])
+                t = timed(lambda it: [StepEntry(("d", i), [(7 * it + i) % vocab], [0]) for i in range(batch)],
+                          max(args.steps // 8, 12))
+                ms = sorted(t[3:])[len(t[3:]) // 2]
+                rec[f"decode_b{batch}"] = {"ms_per_step": round(ms, 4), "tokens_per_s": round(batch / ms * 1e3, 1)}
+                if batch == 8:
+                    kv = 8 * 512 * 2 * width * 2
+                    rec["decode_kernels"] = kernel_table(engine.last_calls, pk, "roofline", attention_bytes=kv,
+                                                         attention_flops=2 * kv)
+                for i in range(batch):
+                    engine.finish(("d", i))
+            out["models"].append(rec)
+            del engine, model
+            torch.cuda.empty_cache()
+    print(json.dumps(out))
+
+
 def main():
     global PAGE_SIZE
     ap = argparse.ArgumentParser()
@@ -651,13 +752,17 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 24 (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline", "kernels", "yardstick"],
+    ap.add_argument("--widths", default="", help="with --only lelatar: the model widths to run, with commas (default 1024,2048)")
+    ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline", "kernels", "yardstick",
+                                                   "lelatar"],
                     help="run just this part and print its figures (decode / prefill: short runs for profiling; "
                          "mixed: 64 requests with prompts of 16..1024 tokens through the scheduler, 256-token portions "
                          "beside decoding requests; timeline: every kernel of one step with its start and end, "
                          "from torch.profiler; kernels: each kind of kernel of a decode and a prefill step timed "
                          "alone, with bytes, flops and the fraction of the measured peak; yardstick: torch.matmul on the "
-                         "model's linear shapes, to hold the hand-written kernels against)")
+                         "model's linear shapes, to hold the hand-written kernels against; lelatar: prefill and decode of "
+                         "the Lelatar design at two widths beside GPT-2 of equal width and layer runs, with every kernel "
+                         "of both against its roofline)")
     ap.add_argument("--prefill-prompts", type=int, default=0,
                     help="with --only prefill: 1024-token prompts in the one step (default and the contract's figure: "
                          "2); with --only timeline: the timeline of such a step instead of a decode step")
@@ -673,6 +778,9 @@ def main():
         print(f"bench.py: this engine runs on one GPU; --gpus {a.gpus} is not offered")
         return 2
     a.warmup = max(a.warmup, 3)
+    if a.only == "lelatar":
+        run_lelatar(a)
+        return 0
     run_ours(a)
     return 0
 

@@ -202,7 +202,7 @@ MLXB_EXPORT int mlxb_attention_generic(int dtype, const void* q, int ldq, const 
                                        const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                                        int Dh, int window, float scale, const void* k_pool, const void* v_pool,
                                        void* out, int ldo, const int* rows, int n_tokens, int* status,
-                                       cudaStream_t stream, const float* sinks) {
+                                       const float* sinks, cudaStream_t stream) {
   if (n_tokens <= 0) return 0;
   if (int e = check_common("attention", page, Hq, Hkv, Dh)) return e;
   const int warps = 4;
@@ -572,8 +572,8 @@ MLXB_EXPORT int mlxb_attention_decode(int dtype, const void* q, int ldq, const i
                                       const int* token_req, const int* block_table, int max_pages, int n_pages,
                                       int page, int Hq, int Hkv, int Dh, int window, float scale, const void* k_pool,
                                       const void* v_pool, float* partial, int* counters, int n_chunks_max, int chunk,
-                                      void* out, int ldo, int n_rows, int* status, cudaStream_t stream,
-                                      const float* sinks) {
+                                      void* out, int ldo, int n_rows, int* status, const float* sinks,
+                                      cudaStream_t stream) {
   if (n_rows <= 0) return 0;
   if (int e = check_common("attention (single-token rows)", page, Hq, Hkv, Dh)) return e;
   if (Dh % 8) return mlxb_fail(MLXB_BAD_ARG, "attention (single-token rows): head size %d is not a multiple of 8", Dh);
@@ -648,5 +648,5 @@ MLXB_EXPORT int mlxb_attention_decode_noalloc(int dtype, const void* q, int ldq,
   return mlxb_attention_decode(dtype, q, ldq, rows, positions, token_req, block_table, max_pages, n_pages, page,
                                n_q_heads, n_kv_heads, head_dim, window, scale, k_pool, v_pool,
                                g_noalloc_partial_ptr[dev], g_noalloc_counters_ptr[dev], n_chunks_max, chunk, out, ldo,
-                               n_rows, status, stream, nullptr);
+                               n_rows, status, nullptr, stream);
 }

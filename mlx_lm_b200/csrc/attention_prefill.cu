@@ -85,7 +85,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
                          const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                          int window, float scale_log2e, const __nv_bfloat16* __restrict__ k_pool,
                          const __nv_bfloat16* __restrict__ v_pool, __nv_bfloat16* __restrict__ out, int ldo,
-                         int* __restrict__ status, const float* __restrict__ sinks) {
+                         int* __restrict__ status, const float* __restrict__ sinks,
+                         const int* __restrict__ first_positions) {
   constexpr int THREADS = QW * 32;            // threads of one group: they gather and use the same key blocks
   constexpr int STRIDE = DH + 8;              // elements per shared-memory row (16 bytes of padding)
   constexpr int KS = DH / 16;                 // k steps of Q K^T
@@ -151,9 +152,11 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
 
   // this group's blocks: kb_first, kb_first + KSPLIT, ... (block indices congruent to `group`)
   const int kb_first = kb_lo + ((group - kb_lo) % KSPLIT + KSPLIT) % KSPLIT;
-  // keys before the tile's first query are older than this step: such a block can be on its way before the
-  // wait for the kernel that wrote this step's queries, keys and values
-  const bool early = kb_first <= kb_hi && (kb_first + 1) * BKV <= pos0;
+  // Keys before the first position this step brings for the request are older than this step: such a block can
+  // be on its way before the wait for the kernel that wrote this step's queries, keys and values.  (The tile's
+  // own first position will not do: a later tile of a long portion has keys of this step before it.)  Without
+  // the list of the requests' first positions nothing is loaded early.
+  const bool early = first_positions != nullptr && kb_first <= kb_hi && (kb_first + 1) * BKV <= first_positions[req];
   if (early) load_block(kb_first, 0);
   pdl_wait();
   q = after_wait(q);
@@ -348,7 +351,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int ldq, const int
 template <int DH, int QW, int KSPLIT>
 static int launch(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table, int max_pages,
                   int n_pages, int page, int Hq, int Hkv, int window, float scale, const void* k_pool,
-                  const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream, const float* sinks) {
+                  const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream, const float* sinks,
+                  const int* first_positions) {
   constexpr int WARPS = QW * KSPLIT;
   size_t smem = (size_t)KSPLIT * 2 * 2 * BKV * (DH + 8) * sizeof(__nv_bfloat16);
   const size_t merge = (size_t)(KSPLIT - 1) * (DH / 8 * 4 + 4) * QW * 32 * sizeof(float);
@@ -362,10 +366,11 @@ static int launch(const void* q, int ldq, const int* tiles, int n_tiles, const i
   launch_pdl(kern, dim3(n_tiles, Hq), dim3(WARPS * 32), smem, stream, (const __nv_bfloat16*)q, ldq,
              (const int4*)tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window,
              scale * 1.4426950408889634f, (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool,
-             (__nv_bfloat16*)out, ldo, status, sinks);
+             (__nv_bfloat16*)out, ldo, status, sinks, first_positions);
   return mlxb_check_launch("attention (portions)");
 }
 
+// first_positions: int32, per block-table row the first position this step brings for that request (null: unknown).
 // bfloat16 only.  q: [*, >= Hq*Dh] at row stride ldq; out: [*, Hq*Dh] at row stride ldo (both strides even,
 // bases 4-byte aligned); tiles: int32 [n_tiles][4], see the kernel; pools [n_pages, Hkv, page, Dh].
 // Dh: a multiple of 16 up to 128; other sizes are refused (the generic kernel takes them).
@@ -373,7 +378,8 @@ static int launch(const void* q, int ldq, const int* tiles, int n_tiles, const i
 MLXB_EXPORT int mlxb_attention_prefill(const void* q, int ldq, const int* tiles, int n_tiles, int tile_rows,
                                        const int* block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                                        int Dh, int window, float scale, const void* k_pool, const void* v_pool,
-                                       void* out, int ldo, int* status, cudaStream_t stream, const float* sinks) {
+                                       void* out, int ldo, int* status, const float* sinks,
+                                       const int* first_positions, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (page <= 0 || (page & (page - 1))) return mlxb_fail(MLXB_BAD_ARG, "attention (portions): page size %d", page);
   if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || Hq > 65535)
@@ -386,9 +392,9 @@ MLXB_EXPORT int mlxb_attention_prefill(const void* q, int ldq, const int* tiles,
   case D:                                                                                                             \
     if (tile_rows == 128)                                                                                             \
       return launch<D, 8, 1>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,   \
-                             k_pool, v_pool, out, ldo, status, stream, sinks);                                        \
+                             k_pool, v_pool, out, ldo, status, stream, sinks, first_positions);                       \
     return launch<D, 4, 2>(q, ldq, tiles, n_tiles, block_table, max_pages, n_pages, page, Hq, Hkv, window, scale,     \
-                           k_pool, v_pool, out, ldo, status, stream, sinks)
+                           k_pool, v_pool, out, ldo, status, stream, sinks, first_positions)
   switch (Dh) {
     GO(16); GO(32); GO(48); GO(64); GO(80); GO(96); GO(112); GO(128);
     default:
@@ -628,7 +634,7 @@ static int launch_rows(const void* q, int ldq, const int* tiles, int n_tiles, co
 MLXB_EXPORT int mlxb_attention_rows(const void* q, int ldq, const int* tiles, int n_tiles, const int* block_table,
                                     int max_pages, int n_pages, int page, int Hq, int Hkv, int Dh, int window,
                                     float scale, const void* k_pool, const void* v_pool, void* out, int ldo,
-                                    int* status, cudaStream_t stream, const float* sinks) {
+                                    int* status, const float* sinks, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (page <= 0 || (page & (page - 1))) return mlxb_fail(MLXB_BAD_ARG, "attention (single rows): page size %d", page);
   if (Hkv <= 0 || Hq <= 0 || Hq % Hkv || Hq > 65535)

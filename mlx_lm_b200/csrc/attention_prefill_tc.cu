@@ -408,8 +408,8 @@ static int make_map(CUtensorMap* map, const void* base, long long rows, int cols
 MLXB_EXPORT int mlxb_attention_prefill_tc(const void* q, int ldq, int n_tokens, const int* tiles, int n_tiles,
                                           const int* block_table, int max_pages, int n_pages, int page, int Hq,
                                           int Hkv, int Dh, int window, float scale, const void* k_pool,
-                                          const void* v_pool, void* out, int ldo, int* status, cudaStream_t stream,
-                                          const float* sinks) {
+                                          const void* v_pool, void* out, int ldo, int* status, const float* sinks,
+                                          cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (Dh != HD) return mlxb_fail(MLXB_BAD_ARG, "attention (portions, tcgen05): head size %d, this kernel takes %d", Dh, HD);
   if (page < 8 || page > TK || (page & (page - 1)))

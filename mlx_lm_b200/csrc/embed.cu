@@ -39,7 +39,7 @@ __global__ void embed_pos_kernel(const int* __restrict__ tok, const int* __restr
 // whose residual stream is float32 whatever its weights are).
 MLXB_EXPORT int mlxb_embed_pos(int dtype, const int* tok, const int* pos, const void* wte, const void* wpe,
                                void* out, int T_, int D, int V, int P, float scale, int* status,
-                               cudaStream_t stream, int out_f32) {
+                               int out_f32, cudaStream_t stream) {
   if (T_ <= 0) return 0;
   if (D <= 0 || V <= 0) return mlxb_fail(MLXB_BAD_ARG, "embed_pos: width %d, vocabulary %d", D, V);
   const int threads = D >= 1024 ? 256 : (D >= 256 ? 128 : 64);

@@ -175,7 +175,7 @@ def _call(libname: str, fname: str, argtypes, *args) -> None:
 # embedding + position add
 
 _EMBED_ARGS = [c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float,
-               c_void_p, c_void_p, c_int]
+               c_void_p, c_int, c_void_p]
 
 
 def embed_pos(tokens, positions, wte, wpe, out, status, stream, scale: float = 1.0) -> None:
@@ -194,7 +194,7 @@ def embed_pos(tokens, positions, wte, wpe, out, status, stream, scale: float = 1
         if wpe.shape[1] != D or not wpe.is_contiguous():
             raise KernelError(f"embed_pos: position table {tuple(wpe.shape)} against width {D}")
     _call("embed", "mlxb_embed_pos", _EMBED_ARGS, dtype_code(wte.dtype), _p(tokens), _p(positions), _p(wte),
-          _p(wpe), _p(out), T, D, wte.shape[0], 0 if wpe is None else wpe.shape[0], scale, _p(status), stream, out_f32)
+          _p(wpe), _p(out), T, D, wte.shape[0], 0 if wpe is None else wpe.shape[0], scale, _p(status), out_f32, stream)
 
 
 def gather_tokens(src, index, dst, status, stream) -> None:
@@ -502,11 +502,11 @@ def attention_generic(q, positions, token_req, block_table, k_pool, v_pool, out,
     _call("attention", "mlxb_attention_generic", _ATTN_ARGS, dtype_code(k_pool.dtype), _p(q), _rows(q, "attention q"),
           _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh,
           window, scale, _p(k_pool), _p(v_pool), _p(out), _rows(out, "attention out"), _p(rows), n, _p(status),
-          stream, _sinks(sinks, n_heads, "attention"))
+          _sinks(sinks, n_heads, "attention"), stream)
 
 
 _PRE_ARGS = [c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
-             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p]
+             c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p]
 
 PREFILL_TILE = int(_os.environ.get("MLXB_PREFILL_TILE", "128"))   # queries per CTA of the attention kernels for portions
 PREFILL_TC = _os.environ.get("MLXB_PREFILL_TC", "1") != "0"         # heads of 64 in tiles of 128 on the tcgen05 kernel
@@ -521,11 +521,18 @@ def attention_portions_supported(dtype, head_dim: int, scale: float = 1.0) -> bo
 
 
 def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out, n_heads: int, scale: float,
-                       window: int, status, stream, tile_rows: int = 0, sinks=None) -> None:
+                       window: int, status, stream, tile_rows: int = 0, sinks=None, first_positions=None) -> None:
     """Causal attention of prompt portions on tensor cores (bfloat16, csrc/attention_prefill.cu).
 
     ``tiles``: int32 device tensor ``[n_tiles, 4]``: first token row of the tile, queries in it (1..64),
-    block-table row of its request, position of its first query."""
+    block-table row of its request, position of its first query.  ``first_positions``: int32, per block-table
+    row the first position this step brings for that request; with it the kernel fetches keys older than the
+    step before it waits for the kernel that wrote this step's."""
+    if first_positions is not None:
+        _need(first_positions, torch.int32, "attention_portions first_positions")
+        if first_positions.numel() < block_table.shape[0]:
+            raise KernelError(f"attention_portions: {first_positions.numel()} first positions for "
+                              f"{block_table.shape[0]} requests")
     n_pages, Hkv, page, Dh = _attn_shapes(q, out, k_pool, n_heads, "attention_portions")
     _need(tiles, torch.int32, "attention_portions tiles")
     if tiles.numel() < 4 * n_tiles:
@@ -536,12 +543,12 @@ def attention_portions(q, tiles, n_tiles: int, block_table, k_pool, v_pool, out,
             and ldq % 8 == 0 and ldo % 8 == 0 and q.data_ptr() % 16 == 0 and out.data_ptr() % 16 == 0):
         _call("attention_prefill_tc", "mlxb_attention_prefill_tc", _PRE_TC_ARGS, _p(q), ldq, q.shape[0], _p(tiles),
               n_tiles, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale,
-              _p(k_pool), _p(v_pool), _p(out), ldo, _p(status), stream, _sinks(sinks, n_heads, "attention_portions"))
+              _p(k_pool), _p(v_pool), _p(out), ldo, _p(status), _sinks(sinks, n_heads, "attention_portions"), stream)
         return
     _call("attention_prefill", "mlxb_attention_prefill", _PRE_ARGS, _p(q), _rows(q, "attention q"), _p(tiles), n_tiles,
           tile_rows, _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
-          _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream,
-          _sinks(sinks, n_heads, "attention_portions"))
+          _p(v_pool), _p(out), _rows(out, "attention out"), _p(status),
+          _sinks(sinks, n_heads, "attention_portions"), _p(first_positions), stream)
 
 
 _ROWS_ARGS = [c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_float,
@@ -581,7 +588,7 @@ def attention_rows(q, tiles, n_rows: int, block_table, k_pool, v_pool, out, n_he
         raise KernelError(f"attention_rows: {tiles.numel()} integers for {n_rows} rows")
     _call("attention_prefill", "mlxb_attention_rows", _ROWS_ARGS, _p(q), _rows(q, "attention q"), _p(tiles), n_rows,
           _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, Dh, window, scale, _p(k_pool),
-          _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), stream, _sinks(sinks, n_heads, "attention_rows"))
+          _p(v_pool), _p(out), _rows(out, "attention out"), _p(status), _sinks(sinks, n_heads, "attention_rows"), stream)
 
 
 _DEC_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
@@ -614,7 +621,7 @@ def attention_decode(q, positions, token_req, block_table, k_pool, v_pool, out, 
     _call("attention", "mlxb_attention_decode", _DEC_ARGS, dtype_code(k_pool.dtype), _p(q), _rows(q, "attention q"),
           _p(rows), _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv,
           Dh, window, scale, _p(k_pool), _p(v_pool), _p(scratch), _p(counters), n_chunks, chunk, _p(out),
-          _rows(out, "attention out"), n, _p(status), stream, _sinks(sinks, n_heads, "attention_decode"))
+          _rows(out, "attention out"), n, _p(status), _sinks(sinks, n_heads, "attention_decode"), stream)
 
 
 # --------------------------------------------------------------------------

@@ -108,7 +108,8 @@ def paged_attention(ctx, q, cache, o, n_heads: int, head_dim: int, scale: float,
     if ctx.n_portion:
         if ops.attention_portions_supported(q.dtype, head_dim, scale) and ctx.portion_tiles is not None:
             ops.attention_portions(q, ctx.portion_tiles, ctx.n_portion_tiles, cache.block_table, cache.k,
-                                   cache.v, o, n_heads, scale, window, ctx.status, ctx.stream, sinks=sinks)
+                                   cache.v, o, n_heads, scale, window, ctx.status, ctx.stream, sinks=sinks,
+                                   first_positions=ctx.req_first_position)
         else:
             ops.attention_generic(q, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o,
                                   n_heads, scale, window, ctx.status, ctx.stream,

@@ -165,7 +165,7 @@ def run_trace(model_dir, trace, dtype, out_dir, max_tokens=None, extra=(), timeo
         if proc.poll() is None:
             proc.kill()
     cfg = json.load(open(os.path.join(model_dir, "config.json")))
-    V = cfg["vocab_size"]
+    V = cfg["vocab_size"] if "vocab_size" in cfg else cfg["vocab"]
     got = {}
     for s, rows in zip(trace.steps, trace.rows):
         path = os.path.join(out_dir, f"{s['step']}.f32")

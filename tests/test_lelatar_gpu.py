@@ -1,0 +1,234 @@
+"""Lelatar through the engine against the plain implementation (tests/plain_lelatar.py): whole prompts, prefill
+against token-by-token decoding, portions down to two tokens, mixed batches with pages and state slots that are
+used again, each mechanism with the others switched off, weights made so that a lost far key, a left-out sink
+or a dropped state would show, sizes that differ in every place, and greedy generation through the entry points."""
+import copy
+
+import numpy as np
+import pytest
+import torch
+
+import plain_lelatar as plain
+from helpers import Trace, max_live_tokens, mixed_schedule, run_trace
+from lelatar_cases import (CONFIG_P, CONFIG_Q, CONFIG_R, ONLY_MAMBA, make_dir, run_engine, tokens, worst)
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q, "R": CONFIG_R, "mamba": ONLY_MAMBA}
+# Largest |difference| as a fraction of max(1, largest |logit| of the row).  float32: measured on a B200 below 2e-5.
+# bfloat16: rounding of every product's inputs; measured 0.01 to 0.03 on these models.  A mechanism left out moves
+# the logits by 0.3 and more (the tests below assert that where they rely on it).
+TOL = {"float32": 1e-4, "bfloat16": 0.08}
+
+
+def reference(config, weights, requests):
+    return {name: plain.forward(config, weights, toks, dtype=torch.float64).float() for name, toks in requests.items()}
+
+
+def load(path, dtype):
+    from mlx_lm_b200.weights import load_model
+    return load_model(str(path), dtype=dtype)[0]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_whole_prompts(name, dtype, tmp_path):
+    """One step per prompt, all logits: also the first tokens of a sequence (lengths 1, 2, 3: the convolutions
+    see zeros before the start, the states start at zero)."""
+    config = CONFIGS[name]
+    weights = make_dir(tmp_path, config, seed=11)
+    reqs = {f"r{n}": tokens(n, config["vocab"], n) for n in (1, 2, 3, 37, 150)}
+    tr = Trace()
+    for rid, toks in reqs.items():
+        tr.whole(rid, toks)
+    got = run_engine(load(tmp_path, dtype), tr)
+    w = worst(got, reference(config, weights, reqs))
+    print(f"whole {name} {dtype}: {w:.3g}")
+    assert w < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", list(CONFIGS))
+def test_every_cutting_gives_the_same_logits(name, dtype, tmp_path):
+    """Prefill then 40 tokens one by one; portions of many sizes (two tokens, one, sizes around the 16 tokens the
+    scans stage at a time, around 32 and 64 rows, more than a tile of 128 queries); mixed batches of unequal requests in
+    a pool with three state slots and few pages, so that both are used again by later requests."""
+    config = CONFIGS[name]
+    weights = make_dir(tmp_path, config, seed=5)
+    V = config["vocab"]
+    reqs = {"a": tokens(70, V, 1), "b": tokens(131, V, 2), "c": tokens(23, V, 3), "d": tokens(300, V, 4), "e": tokens(5, V, 5)}
+    tr = Trace()
+    for rid, toks in reqs.items():
+        tr.bulk_then_single(f"{rid}:tail", toks, tail=40)
+    for rid, toks in reqs.items():
+        tr.portions(f"{rid}:portions", toks, sizes=(2, 1, 15, 2, 16, 17, 3, 33, 2, 37, 64, 2, 130, 1, 31))
+    mixed_schedule(tr, [(f"{rid}:mixed", toks) for rid, toks in reqs.items()], seed=1, max_live=3)
+    mixed_schedule(tr, [(f"{rid}:mixed2", toks) for rid, toks in reversed(list(reqs.items()))], seed=2, max_live=3,
+                   sizes=(2, 1, 1, 48, 1, 16, 1, 2, 37, 1, 1, 9, 130, 1))
+    pool = max_live_tokens(tr, round_to=16)
+    got = run_engine(load(tmp_path, dtype), tr, page_size=16, n_pages=pool // 16, max_requests=3, max_len=512)
+    assert len(got) == 4 * sum(len(t) for t in reqs.values())
+    w = worst(got, reference(config, weights, reqs))
+    print(f"cuttings {name} {dtype}: {w:.3g}")
+    assert w < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_portions_of_33_to_64_rows_again_and_again(dtype, tmp_path):
+    """Steps of 33 to 64 rows run the few-rows products with their longest-running shape between the short kernels
+    of this design; the same schedule twenty times must give the same logits every time."""
+    config = CONFIG_P
+    weights = make_dir(tmp_path, config, seed=9)
+    toks = tokens(140, config["vocab"], 7)
+    ref = reference(config, weights, {"x": toks})
+    from mlx_lm_b200.engine import Engine
+    model = load(tmp_path, dtype)
+    eng = Engine(model, page_size=16, n_pages=32, max_requests=2, max_len=512)
+    first = None
+    for trial in range(20):
+        tr = Trace()
+        tr.portions("x", toks, sizes=(2, 3, 17, 37, 37, 37, 7))
+        got = run_engine(model, tr, engine=eng)
+        assert worst(got, ref) < TOL[dtype], trial
+        flat = np.stack([got[k] for k in sorted(got)])
+        if first is None:
+            first = flat
+        assert np.array_equal(flat, first), f"run {trial} differs from the first"
+
+
+def sharpen(w, factor=6.0):
+    for k in w:
+        if k.endswith(".left.q.norm") or k.endswith(".left.k.norm"):      # q and k are normed: their gains set the sharpness
+            w[k] *= factor ** 0.5
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_sharp_attention_finds_far_keys(dtype, tmp_path):
+    """Queries and keys scaled up so that single scores stand out: a key lost at a page's border, at the border of
+    a 128-key block or far back changes the logits.  Prompts in portions that end at and next to those borders."""
+    config = copy.deepcopy(CONFIG_Q)
+    weights = make_dir(tmp_path, config, seed=21, edit=lambda w: sharpen(w, 40.0))
+    V = config["vocab"]
+    reqs = {"a": tokens(400, V, 31), "b": tokens(260, V, 32)}
+    ref = reference(config, weights, reqs)
+    dull = make_dir(tmp_path / "dull", config, seed=21)     # the same model without the sharpening
+    assert float((plain.forward(config, dull, reqs["b"]).float() - ref["b"]).abs().max()) > 0.5
+    tr = Trace()
+    tr.portions("a:1", reqs["a"], sizes=(127, 1, 2, 126, 16, 15, 1, 112))
+    tr.portions("b:1", reqs["b"], sizes=(129, 127, 2, 2))
+    tr.bulk_then_single("b:2", reqs["b"], tail=8)
+    got = run_engine(load(tmp_path, dtype), tr)
+    w = worst(got, ref)
+    print(f"far keys {dtype}: {w:.3g}")
+    assert w < 2 * TOL[dtype]
+
+
+def test_the_sink_counts_once_and_has_no_value(tmp_path):
+    """Sinks made large: they take most of every softmax.  Left out, or given a value, the logits move."""
+    config = copy.deepcopy(CONFIG_R)
+
+    def edit(w):
+        for k in w:
+            if k.endswith(".sink"):
+                w[k] = torch.linspace(1.0, 4.0, w[k].numel())
+            if k.endswith(".right.out"):
+                w[k] *= 0.0          # the other side of the layer is silent: what is seen is the attention
+    weights = make_dir(tmp_path, config, seed=3, edit=edit)
+    reqs = {"a": tokens(90, config["vocab"], 1)}
+    ref = reference(config, weights, reqs)
+    no_sink = {k: (v - 30.0 if k.endswith(".sink") else v) for k, v in weights.items()}
+    assert float((plain.forward(config, no_sink, reqs["a"]).float() - ref["a"]).abs().max()) > 0.3
+    tr = Trace()
+    tr.whole("a:w", reqs["a"])
+    tr.portions("a:p", reqs["a"], sizes=(3, 40, 2, 1, 1, 1, 17))
+    for dtype in DTYPES:
+        w = worst(run_engine(load(tmp_path, dtype), tr), ref)
+        print(f"sink {dtype}: {w:.3g}")
+        assert w < TOL[dtype]
+
+
+@pytest.mark.parametrize("silent", ["left", "right"])
+def test_each_side_of_a_parallel_layer_alone(silent, tmp_path):
+    config = copy.deepcopy(CONFIG_P)
+
+    def edit(w):
+        for k in w:
+            if k.endswith(f".{silent}.out"):
+                w[k] *= 0.0
+    weights = make_dir(tmp_path, config, seed=17, edit=edit)
+    reqs = {"a": tokens(75, config["vocab"], 2)}
+    ref = reference(config, weights, reqs)
+    tr = Trace()
+    tr.whole("a:w", reqs["a"])
+    tr.bulk_then_single("a:t", reqs["a"], tail=33)
+    w = worst(run_engine(load(tmp_path, "float32"), tr), ref)
+    assert w < TOL["float32"], w
+
+
+def test_state_is_per_request_and_starts_at_zero(tmp_path):
+    """A slot that a long request left is given to the next one: its state must not leak.  The same prompt, run
+    after another request in the same slot, gives the logits it gives in a fresh engine."""
+    config = ONLY_MAMBA
+    weights = make_dir(tmp_path, config, seed=2)
+    V = config["vocab"]
+    a, b = tokens(120, V, 1), tokens(9, V, 2)
+    ref = reference(config, weights, {"a": a, "b": b})
+    tr = Trace()
+    tr.whole("a:1", a)
+    tr.portions("b:1", b, sizes=(2, 1, 3))
+    tr.whole("a:2", a)
+    got = run_engine(load(tmp_path, "float32"), tr, max_requests=1, n_pages=16)
+    assert worst(got, ref) < TOL["float32"]
+
+
+def test_trace_replay_with_few_slots_and_pages(tmp_path):
+    """The command-line replay on this design: mixed steps in a pool that forces pages and slots to be used again."""
+    config = CONFIG_P
+    weights = make_dir(tmp_path / "m", config, seed=13)
+    V = config["vocab"]
+    reqs = {f"r{i}": tokens(n, V, 40 + i) for i, n in enumerate((50, 3, 129, 64, 18, 77))}
+    ref = reference(config, weights, reqs)
+    tr = Trace()
+    mixed_schedule(tr, list(reqs.items()), seed=5, max_live=4)
+    for dtype in DTYPES:
+        got = run_trace(str(tmp_path / "m"), tr, dtype, str(tmp_path / f"out-{dtype}"), extra=("--max-requests", "4"))
+        w = worst(got, ref)
+        print(f"replay {dtype}: {w:.3g}")
+        assert w < TOL[dtype]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_greedy_generation_through_the_entry_points(dtype, tmp_path):
+    """``generate``, ``stream_generate`` and ``batch_generate`` (scheduler, decode graphs, device sampler) give the
+    plain model's greedy tokens."""
+    from mlx_lm_b200 import batch_generate, generate, load, stream_generate
+    config = CONFIG_P
+    weights = make_dir(tmp_path, config, seed=23, edit=lambda w: w.__setitem__("head", w["head"] * 4.0))
+    V = config["vocab"]
+    prompts = [tokens(7, V, 0), tokens(21, V, 1), tokens(2, V, 2)]
+
+    def greedy(prompt, n):
+        seq = list(prompt)
+        for _ in range(n):
+            seq.append(int(plain.forward(config, weights, seq)[-1].argmax()))
+        return seq[len(prompt):]
+
+    def agrees(got, ref, prompt):
+        for i, (a, b) in enumerate(zip(got, ref)):
+            if a != b:
+                lg = plain.forward(config, weights, prompt + ref[:i])[-1]
+                top = torch.topk(lg, 2).values
+                return dtype == "bfloat16" and float(top[0] - top[1]) < 0.05 * float(lg.abs().max())
+        return len(got) == len(ref)
+
+    want = [greedy(p, 12) for p in prompts]
+    model, tokenizer = load(str(tmp_path), dtype=dtype)
+    for p, w in zip(prompts, want):
+        got = [int(t) for t in generate(model, tokenizer, p, max_tokens=12).split()]
+        assert agrees(got, w, p), (got, w)
+        streamed = [r.token for r in stream_generate(model, tokenizer, p, max_tokens=12, prefill_step_size=5)]
+        assert agrees(streamed, w, p), (streamed, w)
+    out = batch_generate(model, tokenizer, prompts, max_tokens=12, return_token_ids=True)
+    for got, w, p in zip(out.token_ids, want, prompts):
+        assert agrees(got, w, p), (got, w)
