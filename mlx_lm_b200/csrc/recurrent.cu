@@ -132,8 +132,12 @@ struct ScanShape {
   int NS, VB, threads, zblocks;
 };
 
-// n_rows: rows of the state (N or K); V: its columns.
-static inline ScanShape scan_shape(int n_rows, int V) {
+// n_rows: rows of the state (N or K); V: its columns; pairs: (request, head) pairs of the launch.  A block takes all
+// columns of a pair when there are pairs enough to fill the SMs; with fewer the columns are cut into several
+// blocks, each of which stages the pair's inputs for itself, but never below four warps a block: a token's
+// update is a chain of dependent instructions, and a warp alone on an SM shows all of their latency (blocks of one
+// warp made the prefill of two prompts slower, not faster).
+static inline ScanShape scan_shape(int n_rows, int V, long long pairs) {
   ScanShape s;
   s.NS = 1;
   while (s.NS * SCAN_NPT < n_rows) s.NS <<= 1;
@@ -141,19 +145,25 @@ static inline ScanShape scan_shape(int n_rows, int V) {
   const int vmax = 512 / s.NS;                       // columns per block at most
   int vb = (V + lanes - 1) / lanes * lanes;
   if (vb > vmax) vb = vmax;
+  const long long want = mlxb_sm_count();
+  while (vb > lanes && pairs * ((V + vb - 1) / vb) < want) {
+    int half = (vb / 2 + lanes - 1) / lanes * lanes;
+    if (half >= vb || half * s.NS < 128) break;
+    vb = half;
+  }
   s.VB = vb;
   s.threads = vb * s.NS;
   s.zblocks = (V + vb - 1) / vb;
   return s;
 }
 
-template <typename T>
-__global__ void __launch_bounds__(512)
+template <typename T, int NS>
+__global__ void __launch_bounds__(512, 1)
 mamba2_scan_kernel(const T* xbc, int ldx, int x_off, int b_off, int c_off, const T* dt_raw, int lddt,
                    const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                    const float* __restrict__ Dskip, float* state, const int* __restrict__ slots,
                    const int* __restrict__ token_req, const int* __restrict__ req_first_token, float* __restrict__ y,
-                   int ldy, int H, int G, int N, int V, int NS, int VB) {
+                   int ldy, int H, int G, int N, int V, int VB) {
   extern __shared__ float sm[];
   float* sB = sm;                          // [CHUNK][N]
   float* sC = sB + SCAN_CHUNK * N;         // [CHUNK][N]
@@ -201,17 +211,19 @@ mamba2_scan_kernel(const T* xbc, int ldx, int x_off, int b_off, int c_off, const
     __syncthreads();
     for (int tt = 0; tt < nc; ++tt) {
       const float a = sa[tt], xv = sx[tt * VB + vl], dtx = sdt[tt] * xv;
-      const float* Bt = sB + tt * N;
-      const float* Ct = sC + tt * N;
-      float acc = 0.f;
+      const float* Bt = sB + tt * N + s;
+      const float* Ct = sC + tt * N + s;
+      float acc0 = 0.f, acc1 = 0.f;      // two chains, added at the end: rows 0, 2, .. and 1, 3, .. of the thread's share
 #pragma unroll
       for (int i = 0; i < SCAN_NPT; ++i) {
-        const int nn = s + i * NS;
-        if (nn < N) {
-          S[i] = fmaf(a, S[i], dtx * Bt[nn]);
-          acc = fmaf(S[i], Ct[nn], acc);
+        if (i * NS < N - s) {
+          S[i] = fmaf(a, S[i], dtx * Bt[i * NS]);
+          if (i & 1) acc1 = fmaf(S[i], Ct[i * NS], acc1);
+          else acc0 = fmaf(S[i], Ct[i * NS], acc0);
         }
       }
+      float acc = acc0 + acc1;
+#pragma unroll
       for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
       if (s == 0 && valid) y[(size_t)(t0 + c0 + tt) * ldy + h * V + v] = fmaf(skip, xv, acc);
     }
@@ -235,36 +247,42 @@ MLXB_EXPORT int mlxb_mamba2_scan(int dtype, const void* xbc, int ldx, int x_off,
   if (H <= 0 || G <= 0 || H % G || N <= 0 || V <= 0 || N > 32 * SCAN_NPT || n_requests > 65535)
     return mlxb_fail(MLXB_BAD_ARG, "mamba2_scan: %d heads in %d groups, state %d x %d (at most %d rows)", H, G, N, V,
                      32 * SCAN_NPT);
-  const ScanShape sh = scan_shape(N, V);
+  const ScanShape sh = scan_shape(N, V, (long long)H * n_requests);
   const size_t smem = (size_t)(SCAN_CHUNK * (2 * N + sh.VB + 2)) * sizeof(float);
   const dim3 grid(H, n_requests, sh.zblocks);
+  if (dtype != MLXB_F32 && dtype != MLXB_BF16) return mlxb_fail(MLXB_BAD_DTYPE, "mamba2_scan: dtype code %d", dtype);
   cudaError_t e = cudaSuccess;
-  if (dtype == MLXB_F32) {
-    if (smem > 48 * 1024) e = cudaFuncSetAttribute(mamba2_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess)
-      launch_pdl(mamba2_scan_kernel<float>, grid, dim3(sh.threads), smem, stream, (const float*)xbc, ldx, x_off, b_off,
-                 c_off, (const float*)dt_raw, lddt, dt_bias, A_log, Dskip, state, slots, token_req, req_first_token, y,
-                 ldy, H, G, N, V, sh.NS, sh.VB);
-  } else if (dtype == MLXB_BF16) {
-    if (smem > 48 * 1024) e = cudaFuncSetAttribute(mamba2_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess)
-      launch_pdl(mamba2_scan_kernel<__nv_bfloat16>, grid, dim3(sh.threads), smem, stream, (const __nv_bfloat16*)xbc, ldx,
-                 x_off, b_off, c_off, (const __nv_bfloat16*)dt_raw, lddt, dt_bias, A_log, Dskip, state, slots,
-                 token_req, req_first_token, y, ldy, H, G, N, V, sh.NS, sh.VB);
-  } else {
-    return mlxb_fail(MLXB_BAD_DTYPE, "mamba2_scan: dtype code %d", dtype);
+#define M2_GO(T_, NS_)                                                                                                   \
+  {                                                                                                                      \
+    if (smem > 48 * 1024)                                                                                                \
+      e = cudaFuncSetAttribute(mamba2_scan_kernel<T_, NS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+    if (e == cudaSuccess)                                                                                                \
+      launch_pdl(mamba2_scan_kernel<T_, NS_>, grid, dim3(sh.threads), smem, stream, (const T_*)xbc, ldx, x_off, b_off,   \
+                 c_off, (const T_*)dt_raw, lddt, dt_bias, A_log, Dskip, state, slots, token_req, req_first_token, y,     \
+                 ldy, H, G, N, V, sh.VB);                                                                                \
   }
+#define M2_NS(NS_) { if (dtype == MLXB_F32) M2_GO(float, NS_) else M2_GO(__nv_bfloat16, NS_) }
+  switch (sh.NS) {
+    case 1: M2_NS(1) break;
+    case 2: M2_NS(2) break;
+    case 4: M2_NS(4) break;
+    case 8: M2_NS(8) break;
+    case 16: M2_NS(16) break;
+    default: M2_NS(32) break;
+  }
+#undef M2_NS
+#undef M2_GO
   if (e != cudaSuccess) return mlxb_fail((int)e, "mamba2_scan: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   return mlxb_check_launch("mamba2_scan");
 }
 
-template <typename T>
-__global__ void __launch_bounds__(512)
+template <typename T, int NS>
+__global__ void __launch_bounds__(512, 1)
 gated_delta_scan_kernel(const T* qkv, int ldq, int q_off, int k_off, int v_off, const T* b_raw, int ldb,
                         const T* a_raw, int lda, const float* __restrict__ dt_bias, const float* __restrict__ A_log,
                         float* state, const int* __restrict__ slots, const int* __restrict__ token_req,
                         const int* __restrict__ req_first_token, float* __restrict__ o, int ldo, int H, int G, int K,
-                        int V, int NS, int VB) {
+                        int V, int VB) {
   extern __shared__ float sm[];
   float* sq = sm;                          // [CHUNK][K]
   float* sk = sq + SCAN_CHUNK * K;         // [CHUNK][K]
@@ -325,28 +343,34 @@ gated_delta_scan_kernel(const T* qkv, int ldq, int q_off, int k_off, int v_off, 
     __syncthreads();
     for (int tt = 0; tt < nc; ++tt) {
       const float gg = sg[tt], beta = sbeta[tt], vv = sv[tt * VB + vl];
-      const float* kt = sk + tt * K;
-      const float* qt = sq + tt * K;
-      float acc = 0.f;
+      const float* kt = sk + tt * K + s;
+      const float* qt = sq + tt * K + s;
+      float kr[SCAN_NPT];
+      float acc0 = 0.f, acc1 = 0.f;      // two chains each, added at the end
 #pragma unroll
       for (int i = 0; i < SCAN_NPT; ++i) {
-        const int kk = s + i * NS;
-        if (kk < K) {
+        if (i * NS < K - s) {
+          kr[i] = kt[i * NS];
           S[i] *= gg;
-          acc = fmaf(S[i], kt[kk], acc);
+          if (i & 1) acc1 = fmaf(S[i], kr[i], acc1);
+          else acc0 = fmaf(S[i], kr[i], acc0);
         }
       }
+      float acc = acc0 + acc1;
+#pragma unroll
       for (int w = NS >> 1; w > 0; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
       const float u = beta * (vv - acc);
-      float out = 0.f;
+      float out0 = 0.f, out1 = 0.f;
 #pragma unroll
       for (int i = 0; i < SCAN_NPT; ++i) {
-        const int kk = s + i * NS;
-        if (kk < K) {
-          S[i] = fmaf(kt[kk], u, S[i]);
-          out = fmaf(S[i], qt[kk], out);
+        if (i * NS < K - s) {
+          S[i] = fmaf(kr[i], u, S[i]);
+          if (i & 1) out1 = fmaf(S[i], qt[i * NS], out1);
+          else out0 = fmaf(S[i], qt[i * NS], out0);
         }
       }
+      float out = out0 + out1;
+#pragma unroll
       for (int w = NS >> 1; w > 0; w >>= 1) out += __shfl_xor_sync(0xffffffffu, out, w);
       if (s == 0 && valid) o[(size_t)(t0 + c0 + tt) * ldo + h * V + v] = out;
     }
@@ -370,25 +394,31 @@ MLXB_EXPORT int mlxb_gated_delta_scan(int dtype, const void* qkv, int ldq, int q
   if (H <= 0 || G <= 0 || H % G || K <= 0 || V <= 0 || K > 32 * SCAN_NPT || n_requests > 65535)
     return mlxb_fail(MLXB_BAD_ARG, "gated_delta_scan: %d heads over %d key heads, state %d x %d (at most %d rows)", H, G,
                      K, V, 32 * SCAN_NPT);
-  const ScanShape sh = scan_shape(K, V);
+  const ScanShape sh = scan_shape(K, V, (long long)H * n_requests);
   const size_t smem = (size_t)(SCAN_CHUNK * (2 * K + sh.VB + 2)) * sizeof(float);
   const dim3 grid(H, n_requests, sh.zblocks);
+  if (dtype != MLXB_F32 && dtype != MLXB_BF16) return mlxb_fail(MLXB_BAD_DTYPE, "gated_delta_scan: dtype code %d", dtype);
   cudaError_t e = cudaSuccess;
-  if (dtype == MLXB_F32) {
-    if (smem > 48 * 1024) e = cudaFuncSetAttribute(gated_delta_scan_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess)
-      launch_pdl(gated_delta_scan_kernel<float>, grid, dim3(sh.threads), smem, stream, (const float*)qkv, ldq, q_off,
-                 k_off, v_off, (const float*)b_raw, ldb, (const float*)a_raw, lda, dt_bias, A_log, state, slots,
-                 token_req, req_first_token, o, ldo, H, G, K, V, sh.NS, sh.VB);
-  } else if (dtype == MLXB_BF16) {
-    if (smem > 48 * 1024) e = cudaFuncSetAttribute(gated_delta_scan_kernel<__nv_bfloat16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-    if (e == cudaSuccess)
-      launch_pdl(gated_delta_scan_kernel<__nv_bfloat16>, grid, dim3(sh.threads), smem, stream, (const __nv_bfloat16*)qkv,
-                 ldq, q_off, k_off, v_off, (const __nv_bfloat16*)b_raw, ldb, (const __nv_bfloat16*)a_raw, lda, dt_bias,
-                 A_log, state, slots, token_req, req_first_token, o, ldo, H, G, K, V, sh.NS, sh.VB);
-  } else {
-    return mlxb_fail(MLXB_BAD_DTYPE, "gated_delta_scan: dtype code %d", dtype);
+#define GD_GO(T_, NS_)                                                                                                    \
+  {                                                                                                                       \
+    if (smem > 48 * 1024)                                                                                                 \
+      e = cudaFuncSetAttribute(gated_delta_scan_kernel<T_, NS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess)                                                                                                 \
+      launch_pdl(gated_delta_scan_kernel<T_, NS_>, grid, dim3(sh.threads), smem, stream, (const T_*)qkv, ldq, q_off,      \
+                 k_off, v_off, (const T_*)b_raw, ldb, (const T_*)a_raw, lda, dt_bias, A_log, state, slots, token_req,     \
+                 req_first_token, o, ldo, H, G, K, V, sh.VB);                                                             \
   }
+#define GD_NS(NS_) { if (dtype == MLXB_F32) GD_GO(float, NS_) else GD_GO(__nv_bfloat16, NS_) }
+  switch (sh.NS) {
+    case 1: GD_NS(1) break;
+    case 2: GD_NS(2) break;
+    case 4: GD_NS(4) break;
+    case 8: GD_NS(8) break;
+    case 16: GD_NS(16) break;
+    default: GD_NS(32) break;
+  }
+#undef GD_NS
+#undef GD_GO
   if (e != cudaSuccess) return mlxb_fail((int)e, "gated_delta_scan: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e));
   return mlxb_check_launch("gated_delta_scan");
 }
