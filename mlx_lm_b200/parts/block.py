@@ -20,6 +20,7 @@ FOLD_NORMS = os.environ.get("MLXB_FOLD_NORMS", "1") != "0"
 
 class PreNormBlock(Block):
     replayable = True
+    kernel_libs = ("gemm_smallm_fold", "norm")     # what folding a norm into a linear layer launches from
     def __init__(self, norm_1: Norm, mixer: Mixer, norm_2: Norm, feed_forward: FeedForward):
         self.norm_1, self.mixer, self.norm_2, self.feed_forward = norm_1, mixer, norm_2, feed_forward
         self._defer_1 = self._defer_2 = False
