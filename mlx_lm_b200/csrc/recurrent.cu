@@ -16,9 +16,10 @@
 //                    q and k divided by sqrt(|.|^2 + 1e-6) (q also by sqrt(dim)), beta = sigmoid(b_raw),
 //                    g = exp(-exp(A_log) softplus(a_raw + dt_bias)); S is [K, V].
 //
-// Both scans give a thread one column v of the state and every NS-th row of it (at most 16 values in
-// registers); the NS threads of a column are neighbouring lanes and add their partial sums by shuffles.
-// The inputs of 16 tokens at a time are staged in shared memory by the whole block.
+// Both scans give a thread one column v of the state and 16 consecutive rows of it, in registers; the NS
+// threads of a column are neighbouring lanes and add their partial sums by shuffles.  The inputs of 16 tokens
+// at a time are staged in shared memory by the whole block, laid out so that a thread fetches its 16 values
+// with four 16-byte loads; four tokens at a time go through the recurrence, their read-outs reduced together.
 #include "common.cuh"
 
 MLXB_DEFINE_LAST_ERROR()
@@ -125,8 +126,10 @@ MLXB_EXPORT int mlxb_conv_silu(int dtype, const void* in, int ldi, const float* 
 
 // ---------------------------------------------------------------- scans
 
-constexpr int SCAN_NPT = 16;     // rows of a state column a thread holds
-constexpr int SCAN_CHUNK = 16;   // tokens staged at a time
+constexpr int SCAN_NPT = 16;               // consecutive rows of a state column a thread holds
+constexpr int SCAN_SEG = SCAN_NPT + 4;     // floats such a run of 16 inputs takes in shared memory: 4 of padding, so that
+                                           // the 16-byte loads of a warp's threads fall on different banks
+constexpr int SCAN_CHUNK = 16;             // tokens staged at a time
 
 struct ScanShape {
   int NS, VB, threads, zblocks;
@@ -134,9 +137,7 @@ struct ScanShape {
 
 // n_rows: rows of the state (N or K); V: its columns; pairs: (request, head) pairs of the launch.  A block takes all
 // columns of a pair when there are pairs enough to fill the SMs; with fewer the columns are cut into several
-// blocks, each of which stages the pair's inputs for itself, but never below four warps a block: a token's
-// update is a chain of dependent instructions, and a warp alone on an SM shows all of their latency (blocks of one
-// warp made the prefill of two prompts slower, not faster).
+// blocks, each of which stages the pair's inputs for itself, but never below four warps a block.
 static inline ScanShape scan_shape(int n_rows, int V, long long pairs) {
   ScanShape s;
   s.NS = 1;
@@ -157,6 +158,19 @@ static inline ScanShape scan_shape(int n_rows, int V, long long pairs) {
   return s;
 }
 
+// where row nn of a token's staged vector lies: runs of SCAN_NPT rows, SCAN_SEG floats apart
+__device__ __forceinline__ int seg_index(int nn) { return (nn / SCAN_NPT) * SCAN_SEG + (nn % SCAN_NPT); }
+
+__device__ __forceinline__ void load16(const float* p, float (&v)[SCAN_NPT]) {
+#pragma unroll
+  for (int j = 0; j < SCAN_NPT / 4; ++j) {
+    const float4 q = reinterpret_cast<const float4*>(p)[j];
+    v[4 * j] = q.x; v[4 * j + 1] = q.y; v[4 * j + 2] = q.z; v[4 * j + 3] = q.w;
+  }
+}
+
+// Thread (s, v) holds rows 16 s .. 16 s + 15 of column v of the state; rows beyond the state's own stay zero (their
+// staged inputs are zeros).  NS threads (neighbouring lanes) share a column.
 template <typename T, int NS>
 __global__ void __launch_bounds__(512, 1)
 mamba2_scan_kernel(const T* xbc, int ldx, int x_off, int b_off, int c_off, const T* dt_raw, int lddt,
@@ -164,10 +178,11 @@ mamba2_scan_kernel(const T* xbc, int ldx, int x_off, int b_off, int c_off, const
                    const float* __restrict__ Dskip, float* state, const int* __restrict__ slots,
                    const int* __restrict__ token_req, const int* __restrict__ req_first_token, float* __restrict__ y,
                    int ldy, int H, int G, int N, int V, int VB) {
-  extern __shared__ float sm[];
-  float* sB = sm;                          // [CHUNK][N]
-  float* sC = sB + SCAN_CHUNK * N;         // [CHUNK][N]
-  float* sx = sC + SCAN_CHUNK * N;         // [CHUNK][VB]
+  extern __shared__ __align__(16) float sm[];
+  constexpr int NP = NS * SCAN_SEG;        // floats of a token's staged B (or C)
+  float* sB = sm;                          // [CHUNK][NP]
+  float* sC = sB + SCAN_CHUNK * NP;        // [CHUNK][NP]
+  float* sx = sC + SCAN_CHUNK * NP;        // [CHUNK][VB]
   float* sdt = sx + SCAN_CHUNK * VB;       // [CHUNK]
   float* sa = sdt + SCAN_CHUNK;            // [CHUNK]
   const int h = blockIdx.x, r = blockIdx.y, vb = blockIdx.z;
@@ -186,51 +201,86 @@ mamba2_scan_kernel(const T* xbc, int ldx, int x_off, int b_off, int c_off, const
   float S[SCAN_NPT];
 #pragma unroll
   for (int i = 0; i < SCAN_NPT; ++i) {
-    const int nn = s + i * NS;
+    const int nn = s * SCAN_NPT + i;
     S[i] = (valid && nn < N) ? st[(size_t)nn * V + v] : 0.f;
   }
   const float negA = -expf(A_log[h]), skip = Dskip[h], bias = dt_bias[h];
   for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
     const int nc = min(SCAN_CHUNK, n - c0);
     __syncthreads();
-    for (int idx = tid; idx < nc * N; idx += nthreads) {
-      const int tt = idx / N, nn = idx - tt * N;
-      const T* row = xbc + (size_t)(t0 + c0 + tt) * ldx;
-      sB[idx] = to_f(row[b_off + g * N + nn]);
-      sC[idx] = to_f(row[c_off + g * N + nn]);
+    // eight elements a thread at a time: their loads go out together, then the stores (one element per
+    // iteration would wait for memory once per element)
+    for (int base = tid; base < nc * NS * SCAN_NPT; base += nthreads * 8) {
+      T bq[8], cq[8];
+      int at[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int idx = base + j * nthreads;
+        const int tt = idx / (NS * SCAN_NPT), nn = idx - tt * (NS * SCAN_NPT);
+        at[j] = (idx < nc * NS * SCAN_NPT && nn < N) ? tt * NP + seg_index(nn) : -1 - (tt * NP + seg_index(nn));
+        if (at[j] >= 0) {
+          const T* row = xbc + (size_t)(t0 + c0 + tt) * ldx;
+          bq[j] = row[b_off + g * N + nn];
+          cq[j] = row[c_off + g * N + nn];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int idx = base + j * nthreads;
+        if (idx < nc * NS * SCAN_NPT) {
+          const int pos = at[j] >= 0 ? at[j] : -1 - at[j];
+          sB[pos] = at[j] >= 0 ? to_f(bq[j]) : 0.f;
+          sC[pos] = at[j] >= 0 ? to_f(cq[j]) : 0.f;
+        }
+      }
     }
     for (int idx = tid; idx < nc * VB; idx += nthreads) {
       const int tt = idx / VB, vv = idx - tt * VB, col = vb * VB + vv;
       sx[idx] = col < V ? to_f(xbc[(size_t)(t0 + c0 + tt) * ldx + x_off + h * V + col]) : 0.f;
     }
-    if (tid < nc) {
-      const float d = softplus_f(to_f(dt_raw[(size_t)(t0 + c0 + tid) * lddt + h]) + bias);
-      sdt[tid] = d;
-      sa[tid] = expf(negA * d);
+    for (int tt = tid; tt < nc; tt += nthreads) {
+      const float d = softplus_f(to_f(dt_raw[(size_t)(t0 + c0 + tt) * lddt + h]) + bias);
+      sdt[tt] = d;
+      sa[tt] = expf(negA * d);
     }
     __syncthreads();
-    for (int tt = 0; tt < nc; ++tt) {
-      const float a = sa[tt], xv = sx[tt * VB + vl], dtx = sdt[tt] * xv;
-      const float* Bt = sB + tt * N + s;
-      const float* Ct = sC + tt * N + s;
-      float acc0 = 0.f, acc1 = 0.f;      // two chains, added at the end: rows 0, 2, .. and 1, 3, .. of the thread's share
+    // Four tokens at a time: the state's update of a token needs only the update before it (one multiply-add
+    // deep), while a token's read-out ends in a chain of shuffles; the four read-outs of a group are reduced
+    // together, so that their latencies overlap instead of adding up.
+    for (int tt0 = 0; tt0 < nc; tt0 += 4) {
+      float acc[4], xs[4];
 #pragma unroll
-      for (int i = 0; i < SCAN_NPT; ++i) {
-        if (i * NS < N - s) {
-          S[i] = fmaf(a, S[i], dtx * Bt[i * NS]);
-          if (i & 1) acc1 = fmaf(S[i], Ct[i * NS], acc1);
-          else acc0 = fmaf(S[i], Ct[i * NS], acc0);
+      for (int u = 0; u < 4; ++u) {
+        const int tt = tt0 + u;
+        const bool in = tt < nc;
+        const int tc = in ? tt : tt0;
+        const float a = in ? sa[tc] : 1.f, xv = sx[tc * VB + vl], dtx = in ? sdt[tc] * xv : 0.f;   // beyond the chunk: S stays
+        float bv[SCAN_NPT], cv[SCAN_NPT];
+        load16(sB + tc * NP + s * SCAN_SEG, bv);
+        load16(sC + tc * NP + s * SCAN_SEG, cv);
+        float acc0 = 0.f, acc1 = 0.f;    // two chains, added at the end: even and odd rows of the thread's share
+#pragma unroll
+        for (int i = 0; i < SCAN_NPT; ++i) {
+          S[i] = fmaf(a, S[i], dtx * bv[i]);
+          if (i & 1) acc1 = fmaf(S[i], cv[i], acc1);
+          else acc0 = fmaf(S[i], cv[i], acc0);
         }
+        acc[u] = acc0 + acc1;
+        xs[u] = xv;
       }
-      float acc = acc0 + acc1;
 #pragma unroll
-      for (int o = NS >> 1; o > 0; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
-      if (s == 0 && valid) y[(size_t)(t0 + c0 + tt) * ldy + h * V + v] = fmaf(skip, xv, acc);
+      for (int o = NS >> 1; o > 0; o >>= 1) {
+#pragma unroll
+        for (int u = 0; u < 4; ++u) acc[u] += __shfl_xor_sync(0xffffffffu, acc[u], o);
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (s == 0 && valid && tt0 + u < nc) y[(size_t)(t0 + c0 + tt0 + u) * ldy + h * V + v] = fmaf(skip, xs[u], acc[u]);
     }
   }
 #pragma unroll
   for (int i = 0; i < SCAN_NPT; ++i) {
-    const int nn = s + i * NS;
+    const int nn = s * SCAN_NPT + i;
     if (valid && nn < N) st[(size_t)nn * V + v] = S[i];
   }
 }
@@ -242,20 +292,24 @@ MLXB_EXPORT int mlxb_mamba2_scan(int dtype, const void* xbc, int ldx, int x_off,
                                  const void* dt_raw, int lddt, const float* dt_bias, const float* A_log,
                                  const float* Dskip, float* state, const int* slots, const int* token_req,
                                  const int* req_first_token, float* y, int ldy, int H, int G, int N, int V,
-                                 int n_requests, cudaStream_t stream) {
+                                 int n_requests, int n_tokens, cudaStream_t stream) {
   if (n_requests <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || N <= 0 || V <= 0 || N > 32 * SCAN_NPT || n_requests > 65535)
     return mlxb_fail(MLXB_BAD_ARG, "mamba2_scan: %d heads in %d groups, state %d x %d (at most %d rows)", H, G, N, V,
                      32 * SCAN_NPT);
   const ScanShape sh = scan_shape(N, V, (long long)H * n_requests);
-  const size_t smem = (size_t)(SCAN_CHUNK * (2 * N + sh.VB + 2)) * sizeof(float);
+  (void)n_tokens;
+  const size_t smem = (size_t)(SCAN_CHUNK * (2 * sh.NS * SCAN_SEG + sh.VB + 2)) * sizeof(float);
   const dim3 grid(H, n_requests, sh.zblocks);
   if (dtype != MLXB_F32 && dtype != MLXB_BF16) return mlxb_fail(MLXB_BAD_DTYPE, "mamba2_scan: dtype code %d", dtype);
   cudaError_t e = cudaSuccess;
 #define M2_GO(T_, NS_)                                                                                                   \
   {                                                                                                                      \
-    if (smem > 48 * 1024)                                                                                                \
+    static size_t allowed = 48 * 1024;   /* per kernel: raised once, outside any stream capture that comes later */     \
+    if (smem > allowed) {                                                                                                \
       e = cudaFuncSetAttribute(mamba2_scan_kernel<T_, NS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
+      if (e == cudaSuccess) allowed = smem;                                                                              \
+    }                                                                                                                    \
     if (e == cudaSuccess)                                                                                                \
       launch_pdl(mamba2_scan_kernel<T_, NS_>, grid, dim3(sh.threads), smem, stream, (const T_*)xbc, ldx, x_off, b_off,   \
                  c_off, (const T_*)dt_raw, lddt, dt_bias, A_log, Dskip, state, slots, token_req, req_first_token, y,     \
@@ -283,10 +337,11 @@ gated_delta_scan_kernel(const T* qkv, int ldq, int q_off, int k_off, int v_off, 
                         float* state, const int* __restrict__ slots, const int* __restrict__ token_req,
                         const int* __restrict__ req_first_token, float* __restrict__ o, int ldo, int H, int G, int K,
                         int V, int VB) {
-  extern __shared__ float sm[];
-  float* sq = sm;                          // [CHUNK][K]
-  float* sk = sq + SCAN_CHUNK * K;         // [CHUNK][K]
-  float* sv = sk + SCAN_CHUNK * K;         // [CHUNK][VB]
+  extern __shared__ __align__(16) float sm[];
+  constexpr int NP = NS * SCAN_SEG;        // floats of a token's staged q (or k)
+  float* sq = sm;                          // [CHUNK][NP]
+  float* sk = sq + SCAN_CHUNK * NP;        // [CHUNK][NP]
+  float* sv = sk + SCAN_CHUNK * NP;        // [CHUNK][VB]
   float* sbeta = sv + SCAN_CHUNK * VB;     // [CHUNK]
   float* sg = sbeta + SCAN_CHUNK;          // [CHUNK]
   const int h = blockIdx.x, r = blockIdx.y, vb = blockIdx.z;
@@ -306,20 +361,52 @@ gated_delta_scan_kernel(const T* qkv, int ldq, int q_off, int k_off, int v_off, 
   float S[SCAN_NPT];
 #pragma unroll
   for (int i = 0; i < SCAN_NPT; ++i) {
-    const int kk = s + i * NS;
+    const int kk = s * SCAN_NPT + i;
     S[i] = (valid && kk < K) ? st[(size_t)kk * V + v] : 0.f;
   }
   const float negA = -expf(A_log[h]), bias = dt_bias[h], q_scale = 1.f / sqrtf((float)K);
   for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
     const int nc = min(SCAN_CHUNK, n - c0);
     __syncthreads();
-    for (int tt = warp; tt < nc; tt += nwarps) {     // a warp per token: load q and k of the head, make them unit vectors
-      const T* row = qkv + (size_t)(t0 + c0 + tt) * ldq;
+    // eight elements a thread at a time: their loads go out together, then the stores
+    for (int base = tid; base < nc * NS * SCAN_NPT; base += nthreads * 8) {
+      T qq[8], kq[8];
+      int at[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int idx = base + j * nthreads;
+        const int tt = idx / (NS * SCAN_NPT), kk = idx - tt * (NS * SCAN_NPT);
+        at[j] = (idx < nc * NS * SCAN_NPT && kk < K) ? tt * NP + seg_index(kk) : -1 - (tt * NP + seg_index(kk));
+        if (at[j] >= 0) {
+          const T* row = qkv + (size_t)(t0 + c0 + tt) * ldq;
+          qq[j] = row[q_off + g * K + kk];
+          kq[j] = row[k_off + g * K + kk];
+        }
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int idx = base + j * nthreads;
+        if (idx < nc * NS * SCAN_NPT) {
+          const int pos = at[j] >= 0 ? at[j] : -1 - at[j];
+          sq[pos] = at[j] >= 0 ? to_f(qq[j]) : 0.f;
+          sk[pos] = at[j] >= 0 ? to_f(kq[j]) : 0.f;
+        }
+      }
+    }
+    for (int idx = tid; idx < nc * VB; idx += nthreads) {
+      const int tt = idx / VB, vv = idx - tt * VB, col = vb * VB + vv;
+      sv[idx] = col < V ? to_f(qkv[(size_t)(t0 + c0 + tt) * ldq + v_off + h * V + col]) : 0.f;
+    }
+    for (int tt = tid; tt < nc; tt += nthreads) {
+      const size_t row = (size_t)(t0 + c0 + tt);
+      sbeta[tt] = 1.f / (1.f + expf(-to_f(b_raw[row * ldb + h])));
+      sg[tt] = expf(negA * softplus_f(to_f(a_raw[row * lda + h]) + bias));
+    }
+    __syncthreads();
+    for (int tt = warp; tt < nc; tt += nwarps) {     // a warp per token: q and k of the head become unit vectors
       float q2 = 0.f, k2 = 0.f;
       for (int kk = lane; kk < K; kk += 32) {
-        const float qv = to_f(row[q_off + g * K + kk]), kv = to_f(row[k_off + g * K + kk]);
-        sq[tt * K + kk] = qv;
-        sk[tt * K + kk] = kv;
+        const float qv = sq[tt * NP + seg_index(kk)], kv = sk[tt * NP + seg_index(kk)];
         q2 = fmaf(qv, qv, q2);
         k2 = fmaf(kv, kv, k2);
       }
@@ -327,57 +414,58 @@ gated_delta_scan_kernel(const T* qkv, int ldq, int q_off, int k_off, int v_off, 
       k2 = warp_sum(k2);
       const float rq = q_scale / sqrtf(q2 + 1e-6f), rk = 1.f / sqrtf(k2 + 1e-6f);
       for (int kk = lane; kk < K; kk += 32) {
-        sq[tt * K + kk] *= rq;
-        sk[tt * K + kk] *= rk;
+        sq[tt * NP + seg_index(kk)] *= rq;
+        sk[tt * NP + seg_index(kk)] *= rk;
       }
     }
-    for (int idx = tid; idx < nc * VB; idx += nthreads) {
-      const int tt = idx / VB, vv = idx - tt * VB, col = vb * VB + vv;
-      sv[idx] = col < V ? to_f(qkv[(size_t)(t0 + c0 + tt) * ldq + v_off + h * V + col]) : 0.f;
-    }
-    if (tid < nc) {
-      const size_t row = (size_t)(t0 + c0 + tid);
-      sbeta[tid] = 1.f / (1.f + expf(-to_f(b_raw[row * ldb + h])));
-      sg[tid] = expf(negA * softplus_f(to_f(a_raw[row * lda + h]) + bias));
-    }
     __syncthreads();
-    for (int tt = 0; tt < nc; ++tt) {
-      const float gg = sg[tt], beta = sbeta[tt], vv = sv[tt * VB + vl];
-      const float* kt = sk + tt * K + s;
-      const float* qt = sq + tt * K + s;
-      float kr[SCAN_NPT];
-      float acc0 = 0.f, acc1 = 0.f;      // two chains each, added at the end
+    // Four tokens at a time.  What the next token waits for is this token's write to S, and that needs the reduced
+    // S^T k; the read-out S^T q is only written out, so its shuffles are put off to the end of the group, where
+    // the four of them overlap.
+    for (int tt0 = 0; tt0 < nc; tt0 += 4) {
+      float outs[4];
 #pragma unroll
-      for (int i = 0; i < SCAN_NPT; ++i) {
-        if (i * NS < K - s) {
-          kr[i] = kt[i * NS];
+      for (int w4 = 0; w4 < 4; ++w4) {
+        const int tt = tt0 + w4;
+        const bool in = tt < nc;
+        const int tc = in ? tt : tt0;
+        const float gg = in ? sg[tc] : 1.f, beta = in ? sbeta[tc] : 0.f, vv = sv[tc * VB + vl];   // beyond the chunk: S stays
+        float kr[SCAN_NPT], qr[SCAN_NPT];
+        load16(sk + tc * NP + s * SCAN_SEG, kr);
+        load16(sq + tc * NP + s * SCAN_SEG, qr);
+        float acc0 = 0.f, acc1 = 0.f;      // two chains each, added at the end
+#pragma unroll
+        for (int i = 0; i < SCAN_NPT; ++i) {
           S[i] *= gg;
           if (i & 1) acc1 = fmaf(S[i], kr[i], acc1);
           else acc0 = fmaf(S[i], kr[i], acc0);
         }
-      }
-      float acc = acc0 + acc1;
+        float acc = acc0 + acc1;
 #pragma unroll
-      for (int w = NS >> 1; w > 0; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
-      const float u = beta * (vv - acc);
-      float out0 = 0.f, out1 = 0.f;
+        for (int w = NS >> 1; w > 0; w >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, w);
+        const float u = beta * (vv - acc);
+        float out0 = 0.f, out1 = 0.f;
 #pragma unroll
-      for (int i = 0; i < SCAN_NPT; ++i) {
-        if (i * NS < K - s) {
+        for (int i = 0; i < SCAN_NPT; ++i) {
           S[i] = fmaf(kr[i], u, S[i]);
-          if (i & 1) out1 = fmaf(S[i], qt[i * NS], out1);
-          else out0 = fmaf(S[i], qt[i * NS], out0);
+          if (i & 1) out1 = fmaf(S[i], qr[i], out1);
+          else out0 = fmaf(S[i], qr[i], out0);
         }
+        outs[w4] = out0 + out1;
       }
-      float out = out0 + out1;
 #pragma unroll
-      for (int w = NS >> 1; w > 0; w >>= 1) out += __shfl_xor_sync(0xffffffffu, out, w);
-      if (s == 0 && valid) o[(size_t)(t0 + c0 + tt) * ldo + h * V + v] = out;
+      for (int w = NS >> 1; w > 0; w >>= 1) {
+#pragma unroll
+        for (int w4 = 0; w4 < 4; ++w4) outs[w4] += __shfl_xor_sync(0xffffffffu, outs[w4], w);
+      }
+#pragma unroll
+      for (int w4 = 0; w4 < 4; ++w4)
+        if (s == 0 && valid && tt0 + w4 < nc) o[(size_t)(t0 + c0 + tt0 + w4) * ldo + h * V + v] = outs[w4];
     }
   }
 #pragma unroll
   for (int i = 0; i < SCAN_NPT; ++i) {
-    const int kk = s + i * NS;
+    const int kk = s * SCAN_NPT + i;
     if (valid && kk < K) st[(size_t)kk * V + v] = S[i];
   }
 }
@@ -389,20 +477,24 @@ MLXB_EXPORT int mlxb_gated_delta_scan(int dtype, const void* qkv, int ldq, int q
                                       const void* b_raw, int ldb, const void* a_raw, int lda, const float* dt_bias,
                                       const float* A_log, float* state, const int* slots, const int* token_req,
                                       const int* req_first_token, float* o, int ldo, int H, int G, int K, int V,
-                                      int n_requests, cudaStream_t stream) {
+                                      int n_requests, int n_tokens, cudaStream_t stream) {
   if (n_requests <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || K <= 0 || V <= 0 || K > 32 * SCAN_NPT || n_requests > 65535)
     return mlxb_fail(MLXB_BAD_ARG, "gated_delta_scan: %d heads over %d key heads, state %d x %d (at most %d rows)", H, G,
                      K, V, 32 * SCAN_NPT);
   const ScanShape sh = scan_shape(K, V, (long long)H * n_requests);
-  const size_t smem = (size_t)(SCAN_CHUNK * (2 * K + sh.VB + 2)) * sizeof(float);
+  (void)n_tokens;
+  const size_t smem = (size_t)(SCAN_CHUNK * (2 * sh.NS * SCAN_SEG + sh.VB + 2)) * sizeof(float);
   const dim3 grid(H, n_requests, sh.zblocks);
   if (dtype != MLXB_F32 && dtype != MLXB_BF16) return mlxb_fail(MLXB_BAD_DTYPE, "gated_delta_scan: dtype code %d", dtype);
   cudaError_t e = cudaSuccess;
 #define GD_GO(T_, NS_)                                                                                                    \
   {                                                                                                                       \
-    if (smem > 48 * 1024)                                                                                                 \
+    static size_t allowed = 48 * 1024;                                                                                    \
+    if (smem > allowed) {                                                                                                 \
       e = cudaFuncSetAttribute(gated_delta_scan_kernel<T_, NS_>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+      if (e == cudaSuccess) allowed = smem;                                                                               \
+    }                                                                                                                     \
     if (e == cudaSuccess)                                                                                                 \
       launch_pdl(gated_delta_scan_kernel<T_, NS_>, grid, dim3(sh.threads), smem, stream, (const T_*)qkv, ldq, q_off,      \
                  k_off, v_off, (const T_*)b_raw, ldb, (const T_*)a_raw, lda, dt_bias, A_log, state, slots, token_req,     \

@@ -802,7 +802,7 @@ def conv_silu(x, weight, bias, state, slots, positions, token_req, req_first_tok
 
 
 _M2_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
 
 
 def mamba2_scan(xbc, x_off: int, b_off: int, c_off: int, dt_raw, dt_bias, a_log, d_skip, state, slots, token_req,
@@ -821,11 +821,11 @@ def mamba2_scan(xbc, x_off: int, b_off: int, c_off: int, dt_raw, dt_bias, a_log,
     _call("recurrent", "mlxb_mamba2_scan", _M2_ARGS, dtype_code(xbc.dtype), _p(xbc), _rows(xbc, "mamba2_scan xbc"), x_off,
           b_off, c_off, _p(dt_raw), _rows(dt_raw, "mamba2_scan dt"), _p(dt_bias), _p(a_log), _p(d_skip), _p(state),
           _p(slots), _p(token_req), _p(req_first_token), _p(y), _rows(y, "mamba2_scan y"), H, n_groups, N, V,
-          slots.numel(), stream)
+          slots.numel(), y.shape[0], stream)
 
 
 _GD_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
 
 
 def gated_delta_scan(qkv, q_off: int, k_off: int, v_off: int, b_raw, a_raw, dt_bias, a_log, state, slots, token_req,
@@ -843,7 +843,7 @@ def gated_delta_scan(qkv, q_off: int, k_off: int, v_off: int, b_raw, a_raw, dt_b
     _call("recurrent", "mlxb_gated_delta_scan", _GD_ARGS, dtype_code(qkv.dtype), _p(qkv), _rows(qkv, "gated_delta qkv"),
           q_off, k_off, v_off, _p(b_raw), _rows(b_raw, "gated_delta b"), _p(a_raw), _rows(a_raw, "gated_delta a"),
           _p(dt_bias), _p(a_log), _p(state), _p(slots), _p(token_req), _p(req_first_token), _p(o),
-          _rows(o, "gated_delta o"), H, n_key_heads, K, V, slots.numel(), stream)
+          _rows(o, "gated_delta o"), H, n_key_heads, K, V, slots.numel(), o.shape[0], stream)
 
 
 # --------------------------------------------------------------------------
