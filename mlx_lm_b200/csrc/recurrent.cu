@@ -11,10 +11,10 @@
 //                    the request's last taps-1 inputs kept in the state (zeros before the sequence starts).
 // conv_state_update  moves the last taps-1 inputs of every run into the state (launched after conv_silu).
 // mamba2_scan        per (request, head): S <- exp(-exp(A_log) dt) S + dt B x^T,  y = S^T C + D x,
-//                    dt = softplus(dt_raw + dt_bias); S is [N, V].
+//                    dt = softplus(dt_raw + dt_bias); S is N x V (kept column by column in the pool).
 // gated_delta_scan   per (request, head): S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q, with
 //                    q and k divided by sqrt(|.|^2 + 1e-6) (q also by sqrt(dim)), beta = sigmoid(b_raw),
-//                    g = exp(-exp(A_log) softplus(a_raw + dt_bias)); S is [K, V].
+//                    g = exp(-exp(A_log) softplus(a_raw + dt_bias)); S is K x V (kept column by column).
 //
 // Both scans give a thread one column v of the state and 16 consecutive rows of it, in registers; the NS
 // threads of a column are neighbouring lanes and add their partial sums by shuffles.  The inputs of 16 tokens
@@ -169,6 +169,36 @@ __device__ __forceinline__ void load16(const float* p, float (&v)[SCAN_NPT]) {
   }
 }
 
+// A thread's 16 rows of its column, to and from the pool.  The pool keeps a head's state column by column
+// ([V][rows]: a thread's rows are consecutive floats, a warp's threads read neighbouring runs), so that a decode
+// step, which is little more than reading and writing every state once, moves whole 16-byte pieces.
+__device__ __forceinline__ void state_load(const float* col, int first, int n_rows, bool valid, float (&S)[SCAN_NPT]) {
+  if ((n_rows & 3) == 0) {
+#pragma unroll
+    for (int j = 0; j < SCAN_NPT / 4; ++j) {
+      float4 q = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (valid && first + 4 * j < n_rows) q = *reinterpret_cast<const float4*>(col + first + 4 * j);
+      S[4 * j] = q.x; S[4 * j + 1] = q.y; S[4 * j + 2] = q.z; S[4 * j + 3] = q.w;
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < SCAN_NPT; ++i) S[i] = (valid && first + i < n_rows) ? col[first + i] : 0.f;
+  }
+}
+__device__ __forceinline__ void state_store(float* col, int first, int n_rows, bool valid, const float (&S)[SCAN_NPT]) {
+  if (!valid) return;
+  if ((n_rows & 3) == 0) {
+#pragma unroll
+    for (int j = 0; j < SCAN_NPT / 4; ++j)
+      if (first + 4 * j < n_rows)
+        *reinterpret_cast<float4*>(col + first + 4 * j) = make_float4(S[4 * j], S[4 * j + 1], S[4 * j + 2], S[4 * j + 3]);
+  } else {
+#pragma unroll
+    for (int i = 0; i < SCAN_NPT; ++i)
+      if (first + i < n_rows) col[first + i] = S[i];
+  }
+}
+
 // Thread (s, v) holds rows 16 s .. 16 s + 15 of column v of the state; rows beyond the state's own stay zero (their
 // staged inputs are zeros).  NS threads (neighbouring lanes) share a column.
 template <typename T, int NS>
@@ -187,23 +217,21 @@ mamba2_scan_kernel(const T* xbc, int ldx, int x_off, int b_off, int c_off, const
   float* sa = sdt + SCAN_CHUNK;            // [CHUNK]
   const int h = blockIdx.x, r = blockIdx.y, vb = blockIdx.z;
   const int t0 = req_first_token[r], t1 = req_first_token[r + 1];
+  const int tid = threadIdx.x, nthreads = blockDim.x;
+  const int s = tid % NS, vl = tid / NS, v = vb * VB + vl;
+  const bool valid = v < V;
+  const int g = h / (H / G);
+  // The state was last written by a step before this one (a cache is touched by one launch a step), so it can
+  // be on its way before the wait for the kernel that wrote this step's inputs.
+  float* st = state + ((size_t)slots[r] * H + h) * N * V + (size_t)(valid ? v : 0) * N;   // this thread's column
+  float S[SCAN_NPT];
+  state_load(st, s * SCAN_NPT, N, valid, S);
   pdl_wait();
   pdl_trigger();
   xbc = after_wait(xbc);
   dt_raw = after_wait(dt_raw);
   const int n = request_rows(token_req, t0, t1, r);
   if (n == 0) return;
-  const int tid = threadIdx.x, nthreads = blockDim.x;
-  const int s = tid % NS, vl = tid / NS, v = vb * VB + vl;
-  const bool valid = v < V;
-  const int g = h / (H / G);
-  float* st = state + ((size_t)slots[r] * H + h) * N * V;
-  float S[SCAN_NPT];
-#pragma unroll
-  for (int i = 0; i < SCAN_NPT; ++i) {
-    const int nn = s * SCAN_NPT + i;
-    S[i] = (valid && nn < N) ? st[(size_t)nn * V + v] : 0.f;
-  }
   const float negA = -expf(A_log[h]), skip = Dskip[h], bias = dt_bias[h];
   for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
     const int nc = min(SCAN_CHUNK, n - c0);
@@ -278,15 +306,11 @@ mamba2_scan_kernel(const T* xbc, int ldx, int x_off, int b_off, int c_off, const
         if (s == 0 && valid && tt0 + u < nc) y[(size_t)(t0 + c0 + tt0 + u) * ldy + h * V + v] = fmaf(skip, xs[u], acc[u]);
     }
   }
-#pragma unroll
-  for (int i = 0; i < SCAN_NPT; ++i) {
-    const int nn = s * SCAN_NPT + i;
-    if (valid && nn < N) st[(size_t)nn * V + v] = S[i];
-  }
+  state_store(st, s * SCAN_NPT, N, valid, S);
 }
 
 // xbc: the convolution's output [n_tokens, ...] (activation dtype) holding x (H*V columns from x_off), B and C (G*N
-// columns each from b_off / c_off); dt_raw: [n_tokens, >= H] at row stride lddt; state: float32 [slots, H, N, V];
+// columns each from b_off / c_off); dt_raw: [n_tokens, >= H] at row stride lddt; state: float32 [slots, H, V, N] (column by column);
 // y: float32 [n_tokens, H*V] at row stride ldy.
 MLXB_EXPORT int mlxb_mamba2_scan(int dtype, const void* xbc, int ldx, int x_off, int b_off, int c_off,
                                  const void* dt_raw, int lddt, const float* dt_bias, const float* A_log,
@@ -346,6 +370,14 @@ gated_delta_scan_kernel(const T* qkv, int ldq, int q_off, int k_off, int v_off, 
   float* sg = sbeta + SCAN_CHUNK;          // [CHUNK]
   const int h = blockIdx.x, r = blockIdx.y, vb = blockIdx.z;
   const int t0 = req_first_token[r], t1 = req_first_token[r + 1];
+  const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
+  const int s = tid % NS, vl = tid / NS, v = vb * VB + vl;
+  const bool valid = v < V;
+  const int g = h / (H / G);
+  // older than this step (see mamba2_scan_kernel): asked for before the wait
+  float* st = state + ((size_t)slots[r] * H + h) * K * V + (size_t)(valid ? v : 0) * K;   // this thread's column
+  float S[SCAN_NPT];
+  state_load(st, s * SCAN_NPT, K, valid, S);
   pdl_wait();
   pdl_trigger();
   qkv = after_wait(qkv);
@@ -353,17 +385,6 @@ gated_delta_scan_kernel(const T* qkv, int ldq, int q_off, int k_off, int v_off, 
   a_raw = after_wait(a_raw);
   const int n = request_rows(token_req, t0, t1, r);
   if (n == 0) return;
-  const int tid = threadIdx.x, nthreads = blockDim.x, lane = tid & 31, warp = tid >> 5, nwarps = nthreads >> 5;
-  const int s = tid % NS, vl = tid / NS, v = vb * VB + vl;
-  const bool valid = v < V;
-  const int g = h / (H / G);
-  float* st = state + ((size_t)slots[r] * H + h) * K * V;
-  float S[SCAN_NPT];
-#pragma unroll
-  for (int i = 0; i < SCAN_NPT; ++i) {
-    const int kk = s * SCAN_NPT + i;
-    S[i] = (valid && kk < K) ? st[(size_t)kk * V + v] : 0.f;
-  }
   const float negA = -expf(A_log[h]), bias = dt_bias[h], q_scale = 1.f / sqrtf((float)K);
   for (int c0 = 0; c0 < n; c0 += SCAN_CHUNK) {
     const int nc = min(SCAN_CHUNK, n - c0);
@@ -463,15 +484,11 @@ gated_delta_scan_kernel(const T* qkv, int ldq, int q_off, int k_off, int v_off, 
         if (s == 0 && valid && tt0 + w4 < nc) o[(size_t)(t0 + c0 + tt0 + w4) * ldo + h * V + v] = outs[w4];
     }
   }
-#pragma unroll
-  for (int i = 0; i < SCAN_NPT; ++i) {
-    const int kk = s * SCAN_NPT + i;
-    if (valid && kk < K) st[(size_t)kk * V + v] = S[i];
-  }
+  state_store(st, s * SCAN_NPT, K, valid, S);
 }
 
 // qkv: the convolutions' output [n_tokens, ...] (activation dtype): q and k (G*K columns each from q_off / k_off),
-// v (H*V columns from v_off); b_raw, a_raw: [n_tokens, >= H] at row strides ldb / lda; state: float32 [slots, H, K, V];
+// v (H*V columns from v_off); b_raw, a_raw: [n_tokens, >= H] at row strides ldb / lda; state: float32 [slots, H, V, K] (column by column);
 // o: float32 [n_tokens, H*V] at row stride ldo.
 MLXB_EXPORT int mlxb_gated_delta_scan(int dtype, const void* qkv, int ldq, int q_off, int k_off, int v_off,
                                       const void* b_raw, int ldb, const void* a_raw, int lda, const float* dt_bias,

@@ -809,11 +809,12 @@ def mamba2_scan(xbc, x_off: int, b_off: int, c_off: int, dt_raw, dt_bias, a_log,
                 req_first_token, y, n_heads: int, n_groups: int, stream) -> None:
     """The selective state-space recurrence per (request, head): ``S <- exp(-exp(A_log) dt) S + dt B x^T``,
     ``y = S^T C + D x`` with ``dt = softplus(dt_raw + dt_bias)``.  ``xbc [T, .]`` holds x, B, C from the given
-    column offsets; ``state`` float32 ``[slots, heads, N, V]``; ``y`` float32 ``[T, heads*V]``."""
+    column offsets; ``state`` float32 ``[slots, heads, V, N]`` (a head's ``N x V`` state column by column); ``y``
+    float32 ``[T, heads*V]``."""
     _need(xbc, dt_raw.dtype, "mamba2_scan xbc")
     _need(state, torch.float32, "mamba2_scan state")
     _need(y, torch.float32, "mamba2_scan y")
-    _, H, N, V = state.shape
+    _, H, V, N = state.shape
     if H != n_heads or y.shape[1] != H * V or not state.is_contiguous():
         raise KernelError(f"mamba2_scan: state {tuple(state.shape)} for {n_heads} heads, y {tuple(y.shape)}")
     for t in (dt_bias, a_log, d_skip):
@@ -832,12 +833,13 @@ def gated_delta_scan(qkv, q_off: int, k_off: int, v_off: int, b_raw, a_raw, dt_b
                      req_first_token, o, n_heads: int, n_key_heads: int, stream) -> None:
     """The gated delta rule per (request, head): ``S <- g S; u = beta (v - S^T k); S <- S + k u^T; o = S^T q`` with
     q and k made unit vectors (q also divided by sqrt(dim)), ``beta = sigmoid(b_raw)``,
-    ``g = exp(-exp(A_log) softplus(a_raw + dt_bias))``.  ``state`` float32 ``[slots, heads, K, V]``; ``o`` float32."""
+    ``g = exp(-exp(A_log) softplus(a_raw + dt_bias))``.  ``state`` float32 ``[slots, heads, V, K]`` (a head's
+    ``K x V`` state column by column); ``o`` float32."""
     _need(state, torch.float32, "gated_delta_scan state")
     _need(o, torch.float32, "gated_delta_scan o")
     _need(b_raw, qkv.dtype, "gated_delta_scan b")
     _need(a_raw, qkv.dtype, "gated_delta_scan a")
-    _, H, K, V = state.shape
+    _, H, V, K = state.shape
     if H != n_heads or o.shape[1] != H * V or not state.is_contiguous():
         raise KernelError(f"gated_delta_scan: state {tuple(state.shape)} for {n_heads} heads, o {tuple(o.shape)}")
     _call("recurrent", "mlxb_gated_delta_scan", _GD_ARGS, dtype_code(qkv.dtype), _p(qkv), _rows(qkv, "gated_delta qkv"),

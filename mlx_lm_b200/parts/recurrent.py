@@ -45,7 +45,7 @@ class Mamba2Mixer(Mixer):
 
     def cache_spec(self):
         return {"conv": StateSpec((self.taps - 1, self.conv_width)),
-                "ssm": StateSpec((self.n_heads, self.state, self.vdim))}
+                "ssm": StateSpec((self.n_heads, self.vdim, self.state))}     # column by column: the scan's layout
 
     def param_specs(self) -> List[ParamSpec]:
         n, H = self.name, self.n_heads
@@ -73,7 +73,9 @@ class Mamba2Mixer(Mixer):
                       conv_state.slots, ctx.positions, ctx.token_req, ctx.req_first_token, ctx.req_first_position, xbc,
                       ctx.stream)
         y = ctx.ws.get("ssm_y", T, inner, torch.float32)
-        ops.label(self.name + ".scan", 6.0 * T * inner * self.state, x.element_size() * T * self.conv_width + 4.0 * T * inner)
+        # what it has to move: its inputs and outputs, and every live request's state in and out
+        ops.label(self.name + ".scan", 6.0 * T * inner * self.state, x.element_size() * T * self.conv_width + 4.0 * T * inner
+                  + 8.0 * min(T, ctx.n_requests) * inner * self.state)
         ops.mamba2_scan(xbc, 0, inner, inner + GN, proj[:, inner + self.conv_width:], self.dt_bias, self.a_log,
                         self.d_skip, ssm_state.state, ssm_state.slots, ctx.token_req, ctx.req_first_token, y,
                         self.n_heads, self.groups, ctx.stream)
@@ -118,7 +120,7 @@ class GatedDeltaMixer(Mixer):
 
     def cache_spec(self):
         return {"conv": StateSpec((self.taps - 1, self.conv_width)),
-                "rule": StateSpec((self.n_heads, self.dim, self.vdim))}
+                "rule": StateSpec((self.n_heads, self.vdim, self.dim))}      # column by column: the scan's layout
 
     def param_specs(self) -> List[ParamSpec]:
         n, H = self.name, self.n_heads
@@ -147,7 +149,8 @@ class GatedDeltaMixer(Mixer):
         g_off = self.conv_width
         b_off = g_off + self.v_width
         o = ctx.ws.get("delta_o", T, self.v_width, torch.float32)
-        ops.label(self.name + ".scan", 8.0 * T * self.v_width * self.dim, x.element_size() * T * self.conv_width + 4.0 * T * self.v_width)
+        ops.label(self.name + ".scan", 8.0 * T * self.v_width * self.dim, x.element_size() * T * self.conv_width + 4.0 * T * self.v_width
+                  + 8.0 * min(T, ctx.n_requests) * self.v_width * self.dim)
         ops.gated_delta_scan(qkv, 0, self.qk_width, 2 * self.qk_width, proj[:, b_off:b_off + H],
                              proj[:, b_off + H:b_off + 2 * H], self.dt_bias, self.a_log, rule_state.state,
                              rule_state.slots, ctx.token_req, ctx.req_first_token, o, H, self.n_kv_heads, ctx.stream)

@@ -71,7 +71,7 @@ def test_a_looped_span_runs_again_with_caches_of_its_own():
     specs = d.cache_specs()
     assert {k[0] for k in specs} == {0, 1, 2, 3, 4, 5, 6, 7}
     assert specs[(2, "left")] == specs[(5, "left")] == PagedKVSpec(1, 64, None)
-    assert specs[(7, "right.rule")] == StateSpec((2, 32, 48)) and specs[(4, "conv")] == StateSpec((2, 4 * 24 + 2 * 4 * 8))
+    assert specs[(7, "right.rule")] == StateSpec((2, 48, 32)) and specs[(4, "conv")] == StateSpec((2, 4 * 24 + 2 * 4 * 8))
     assert sum(isinstance(e, Reentry) for e in describe(CONFIG_R).order) == 0
 
 

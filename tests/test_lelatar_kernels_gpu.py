@@ -79,7 +79,7 @@ def test_state_space_scan(act, H, G, N, V):
     for t in range(T):
         S = a[t, :, None, None] * S + dt[t, :, None, None] * B[t, grp][:, :, None] * x[t, :, None, :]
         want[t] = torch.einsum("hnv,hn->hv", S, C[t, grp]) + d_skip.double()[:, None] * x[t]
-    state = torch.zeros(2, H, N, V, device=DEV)
+    state = torch.zeros(2, H, V, N, device=DEV)          # the pool keeps a head's state column by column
     slots = torch.tensor([1], dtype=torch.int32, device=DEV)
     got = torch.zeros(T, inner, device=DEV)
     xd, dd = xbc.to(DEV), dt_raw.to(DEV)
@@ -92,7 +92,7 @@ def test_state_space_scan(act, H, G, N, V):
         got[lo:hi] = y
     run_in_steps(T, (1, 16, 2, 17, 1, 33), step)
     assert float((got.double().cpu().reshape(T, H, V) - want).abs().max()) < 1e-4 * max(1.0, float(want.abs().max()))
-    assert float((state[1].double().cpu() - S).abs().max()) < 1e-4 * max(1.0, float(S.abs().max()))
+    assert float((state[1].double().cpu().transpose(1, 2) - S).abs().max()) < 1e-4 * max(1.0, float(S.abs().max()))
     assert float(state[0].abs().max()) == 0.0          # the other slot was not touched
 
 
@@ -121,7 +121,7 @@ def test_gated_delta_scan(act, H, G, K, V):
         u = beta[t, :, None] * (v[t] - torch.einsum("hkv,hk->hv", S, kt))
         S = S + kt[:, :, None] * u[:, None, :]
         want[t] = torch.einsum("hkv,hk->hv", S, qt)
-    state = torch.zeros(1, H, K, V, device=DEV)
+    state = torch.zeros(1, H, V, K, device=DEV)
     slots = torch.tensor([0], dtype=torch.int32, device=DEV)
     got = torch.zeros(T, H * V, device=DEV)
     qd, bd, ad = qkv.to(DEV), b_raw.to(DEV), a_raw.to(DEV)
