@@ -44,6 +44,21 @@ CONFIG_Q = {"architecture": "Lelatar", "vocab": 200, "width": 96, "norm": {"eps"
 CONFIG_R = {"architecture": "Lelatar", "vocab": 64, "width": 48, "norm": {"eps": 1e-5}, "token_side": {"dim": 4},
             "layers": [parallel(left(dim=16, heads=3, kv_heads=3, vdim=32, rot_dims=0, scale=0.3),
                                 right(conv=2, dim=24, heads=3, kv_heads=1, vdim=16))]}
+# heads of 48 (stored 48 wide), three groups, a span in the middle that runs twice, five layers
+CONFIG_S = {"architecture": "Lelatar", "vocab": 300, "width": 192, "norm": {"eps": 1e-5}, "token_side": {"dim": 24},
+            "loop": {"start": 1, "stop": 3, "times": 2},
+            "layers": [mamba(conv=4, groups=3, heads=6, norm_groups=3, state=64, vdim=32),
+                       parallel(left(dim=48, heads=6, kv_heads=3, vdim=48, rot_dims=24, base=500000.0, scale=0.15),
+                                right(conv=3, dim=48, heads=6, kv_heads=2, vdim=16), mlp=DENSE(256)),
+                       mamba(conv=4, groups=3, heads=6, norm_groups=3, state=64, vdim=32, mlp=DENSE(256)),
+                       parallel(left(dim=48, heads=6, kv_heads=3, vdim=48, rot_dims=24, base=500000.0, scale=0.15),
+                                right(conv=3, dim=48, heads=6, kv_heads=2, vdim=16)),
+                       mamba(conv=4, groups=3, heads=6, norm_groups=3, state=64, vdim=32)]}
+# wide heads and a large state: 128-wide attention heads, a state of 256 rows (sixteen threads a column)
+CONFIG_T = {"architecture": "Lelatar", "vocab": 128, "width": 128, "norm": {"eps": 1e-5},
+            "layers": [mamba(conv=4, groups=1, heads=2, norm_groups=2, state=256, vdim=16),
+                       parallel(left(dim=128, heads=2, kv_heads=1, vdim=96, rot_dims=64, base=10000.0, scale=0.09),
+                                right(conv=4, dim=128, heads=2, kv_heads=2, vdim=64), mlp=DENSE(192))]}
 ONLY_MAMBA = {"architecture": "Lelatar", "vocab": 64, "width": 48, "norm": {"eps": 1e-5},
               "layers": [mamba(conv=4, groups=2, heads=6, norm_groups=3, state=20, vdim=8)]}
 

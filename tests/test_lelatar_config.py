@@ -6,7 +6,7 @@ import pytest
 import torch
 
 import plain_lelatar as plain
-from lelatar_cases import CONFIG_P, CONFIG_Q, CONFIG_R, ONLY_MAMBA, tokens
+from lelatar_cases import CONFIG_P, CONFIG_Q, CONFIG_R, CONFIG_S, CONFIG_T, ONLY_MAMBA, tokens
 from mlx_lm_b200.cache import CacheManager
 from mlx_lm_b200.config import ConfigError, get_architecture
 from mlx_lm_b200.parts import PagedKVSpec, Reentry, RunEntry, StateSpec
@@ -93,7 +93,7 @@ def test_blocks_with_several_named_caches_in_the_manager():
     mgr.check()
 
 
-@pytest.mark.parametrize("config", [CONFIG_P, CONFIG_Q, CONFIG_R, ONLY_MAMBA])
+@pytest.mark.parametrize("config", [CONFIG_P, CONFIG_Q, CONFIG_R, CONFIG_S, CONFIG_T, ONLY_MAMBA])
 def test_the_plain_model_is_causal(config):
     """Logits at a position do not change when tokens are appended (the plain implementation against itself)."""
     w = random_tensors(describe(config), seed=3)

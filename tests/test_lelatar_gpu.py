@@ -10,12 +10,13 @@ import torch
 
 import plain_lelatar as plain
 from helpers import Trace, max_live_tokens, mixed_schedule, run_trace
-from lelatar_cases import (CONFIG_P, CONFIG_Q, CONFIG_R, ONLY_MAMBA, make_dir, run_engine, tokens, worst)
+from lelatar_cases import (CONFIG_P, CONFIG_Q, CONFIG_R, CONFIG_S, CONFIG_T, ONLY_MAMBA, make_dir, run_engine, tokens,
+                           worst)
 
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q, "R": CONFIG_R, "mamba": ONLY_MAMBA}
+CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q, "R": CONFIG_R, "S": CONFIG_S, "T": CONFIG_T, "mamba": ONLY_MAMBA}
 # Largest |difference| as a fraction of max(1, largest |logit| of the row).  float32: measured on a B200 below 2e-5.
 # bfloat16: rounding of every product's inputs; measured 0.01 to 0.03 on these models.  A mechanism left out moves
 # the logits by 0.3 and more (the tests below assert that where they rely on it).
