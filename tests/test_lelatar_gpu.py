@@ -17,10 +17,12 @@ pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
 CONFIGS = {"P": CONFIG_P, "Q": CONFIG_Q, "R": CONFIG_R, "S": CONFIG_S, "T": CONFIG_T, "mamba": ONLY_MAMBA}
-# Largest |difference| as a fraction of max(1, largest |logit| of the row).  float32: measured on a B200 below 2e-5.
-# bfloat16: rounding of every product's inputs; measured 0.01 to 0.03 on these models.  A mechanism left out moves
-# the logits by 0.3 and more (the tests below assert that where they rely on it).
-TOL = {"float32": 1e-4, "bfloat16": 0.08}
+# Largest |difference| as a fraction of max(1, largest |logit| of the row).  float32: measured on a B200 at most
+# 2.3e-6 over all cases below (2.3e-5 with sharpened attention, which has twice the limit).  bfloat16: rounding of
+# every product's inputs; measured 0.004 to 0.037 (0.12 with sharpened attention).  A mechanism left out moves the
+# logits by 0.3 and more (the tests below assert that where they rely on it); the second tile of a long portion
+# read before its keys were written showed as 0.1 to 0.3.
+TOL = {"float32": 3e-5, "bfloat16": 0.06}
 
 
 def reference(config, weights, requests):
@@ -122,7 +124,7 @@ def test_sharp_attention_finds_far_keys(dtype, tmp_path):
     got = run_engine(load(tmp_path, dtype), tr)
     w = worst(got, ref)
     print(f"far keys {dtype}: {w:.3g}")
-    assert w < 2 * TOL[dtype]
+    assert w < (2 if dtype == "float32" else 3) * TOL[dtype]
 
 
 def test_the_sink_counts_once_and_has_no_value(tmp_path):
