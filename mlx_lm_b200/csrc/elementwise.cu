@@ -21,6 +21,25 @@ __global__ void gated_unit_kernel(const T* in, int ldi, T* __restrict__ out, int
   out[(size_t)t * ldo + j] = from_f<T>(silu_f(to_f(row[j])) * to_f(row[F + j]));
 }
 
+// Eight elements a thread (bfloat16 rows whose halves, strides and bases allow 16-byte accesses).
+__global__ void gated_unit_bf16x8_kernel(const __nv_bfloat16* in, int ldi, __nv_bfloat16* __restrict__ out, int ldo, int F,
+                                         int n) {
+  pdl_wait();
+  pdl_trigger();
+  in = after_wait(in);
+  const int per_row = F / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * per_row) return;
+  const int t = (int)(idx / per_row), j = (int)(idx - (long long)t * per_row) * 8;
+  const __nv_bfloat16* row = in + (size_t)t * ldi;
+  float g[8], u[8], o[8];
+  unpack8(*reinterpret_cast<const uint4*>(row + j), g);
+  unpack8(*reinterpret_cast<const uint4*>(row + F + j), u);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) o[e] = silu_f(g[e]) * u[e];
+  *reinterpret_cast<uint4*>(out + (size_t)t * ldo + j) = pack8(o);
+}
+
 MLXB_EXPORT int mlxb_gated_unit(int dtype, const void* in, int ldi, void* out, int ldo, int F, int n_rows,
                                 cudaStream_t stream) {
   if (n_rows <= 0) return 0;
@@ -30,6 +49,9 @@ MLXB_EXPORT int mlxb_gated_unit(int dtype, const void* in, int ldi, void* out, i
   const dim3 grid((unsigned)((total + threads - 1) / threads));
   if (dtype == MLXB_F32)
     launch_pdl(gated_unit_kernel<float>, grid, dim3(threads), 0, stream, (const float*)in, ldi, (float*)out, ldo, F, n_rows);
+  else if (dtype == MLXB_BF16 && F % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0)
+    launch_pdl(gated_unit_bf16x8_kernel, dim3((unsigned)((total / 8 + threads - 1) / threads)), dim3(threads), 0, stream,
+               (const __nv_bfloat16*)in, ldi, (__nv_bfloat16*)out, ldo, F, n_rows);
   else if (dtype == MLXB_BF16)
     launch_pdl(gated_unit_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)in, ldi,
                (__nv_bfloat16*)out, ldo, F, n_rows);
@@ -89,6 +111,22 @@ __global__ void join_rows_kernel(const float* a, const float* b, int D, T* __res
   out[(size_t)t * ldo + j] = from_f<T>(v);
 }
 
+// Eight elements a thread into bfloat16 rows (D a multiple of 8, 16-byte aligned bases and strides).
+__global__ void join_rows_bf16x8_kernel(const float* a, const float* b, int D, __nv_bfloat16* __restrict__ out, int ldo, int n) {
+  pdl_wait();
+  pdl_trigger();
+  a = after_wait(a);
+  b = after_wait(b);
+  const int W = b ? 2 * D : D, per_row = W / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * per_row) return;
+  const int t = (int)(idx / per_row), j = (int)(idx - (long long)t * per_row) * 8;
+  const float* src = j < D ? a + (size_t)t * D + j : b + (size_t)t * D + j - D;
+  const float4 lo = *reinterpret_cast<const float4*>(src), hi = *reinterpret_cast<const float4*>(src + 4);
+  const float v[8] = {lo.x, lo.y, lo.z, lo.w, hi.x, hi.y, hi.z, hi.w};
+  *reinterpret_cast<uint4*>(out + (size_t)t * ldo + j) = pack8(v);
+}
+
 // a, b: float32 [n_rows, D] contiguous (b may be null); out: [n_rows, D or 2D] at row stride ldo.
 MLXB_EXPORT int mlxb_join_rows(int dtype, const float* a, const float* b, int D, void* out, int ldo, int n_rows,
                                cudaStream_t stream) {
@@ -100,6 +138,10 @@ MLXB_EXPORT int mlxb_join_rows(int dtype, const float* a, const float* b, int D,
   const dim3 grid((unsigned)((total + threads - 1) / threads));
   if (dtype == MLXB_F32)
     launch_pdl(join_rows_kernel<float>, grid, dim3(threads), 0, stream, a, b, D, (float*)out, ldo, n_rows);
+  else if (dtype == MLXB_BF16 && D % 8 == 0 && ldo % 8 == 0 &&
+           (((uintptr_t)a | (uintptr_t)b | (uintptr_t)out) & 15) == 0)
+    launch_pdl(join_rows_bf16x8_kernel, dim3((unsigned)((total / 8 + threads - 1) / threads)), dim3(threads), 0, stream, a, b,
+               D, (__nv_bfloat16*)out, ldo, n_rows);
   else if (dtype == MLXB_BF16)
     launch_pdl(join_rows_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, a, b, D, (__nv_bfloat16*)out, ldo, n_rows);
   else

@@ -63,6 +63,72 @@ __global__ void conv_silu_kernel(const T* in, int ldi, const float* __restrict__
   out[(size_t)t * ldo + c] = from_f<T>(silu_f(acc));
 }
 
+// The same with VEC = 16 / sizeof(T) neighbouring channels a thread and 16-byte accesses (C, the strides and the
+// bases must allow them); a channel's taps are added in the same order, so the results are the same bits.  It
+// reads the weights tap by tap ([taps, C]: neighbouring channels side by side), a copy the caller keeps.
+template <typename T>
+struct Vec16;
+template <>
+struct Vec16<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float (&v)[4]) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+  __device__ static void store(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <>
+struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) { unpack8(*reinterpret_cast<const uint4*>(p), v); }
+  __device__ static void store(__nv_bfloat16* p, const float (&v)[8]) { *reinterpret_cast<uint4*>(p) = pack8(v); }
+};
+
+template <typename T>
+__global__ void conv_silu_vec_kernel(const T* in, int ldi, const float* __restrict__ wt, const float* __restrict__ bias,
+                                     int taps, int C, const float* state, const int* __restrict__ slots,
+                                     const int* __restrict__ positions, const int* __restrict__ token_req,
+                                     const int* __restrict__ req_first_position, T* __restrict__ out, int ldo) {
+  constexpr int VEC = Vec16<T>::N;
+  const int t = blockIdx.y, c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+  const int r = token_req[t];
+  if (r < 0 || c >= C) return;
+  const int i = positions[t] - req_first_position[r];
+  const int slot = slots[r];
+  pdl_wait();
+  pdl_trigger();
+  in = after_wait(in);
+  state = after_wait(state);
+  float acc[VEC];
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = bias ? bias[c + e] : 0.f;
+  for (int j = 0; j < taps; ++j) {
+    float v[VEC];
+    if (j <= i) {
+      Vec16<T>::load(in + (size_t)(t - j) * ldi + c, v);
+    } else {
+      const float* sp = state + ((size_t)slot * (taps - 1) + (taps - 1 + i - j)) * C + c;
+#pragma unroll
+      for (int e = 0; e < VEC; e += 4) {
+        const float4 q = *reinterpret_cast<const float4*>(sp + e);
+        v[e] = q.x; v[e + 1] = q.y; v[e + 2] = q.z; v[e + 3] = q.w;
+      }
+    }
+    const float* wp = wt + (size_t)(taps - 1 - j) * C + c;
+#pragma unroll
+    for (int e = 0; e < VEC; e += 4) {
+      const float4 q = __ldg(reinterpret_cast<const float4*>(wp + e));
+      acc[e] = fmaf(q.x, v[e], acc[e]);
+      acc[e + 1] = fmaf(q.y, v[e + 1], acc[e + 1]);
+      acc[e + 2] = fmaf(q.z, v[e + 2], acc[e + 2]);
+      acc[e + 3] = fmaf(q.w, v[e + 3], acc[e + 3]);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < VEC; ++e) acc[e] = silu_f(acc[e]);
+  Vec16<T>::store(out + (size_t)t * ldo + c, acc);
+}
+
 template <typename T>
 __global__ void conv_state_update_kernel(const T* in, int ldi, int taps, int C, float* state,
                                          const int* __restrict__ slots, const int* __restrict__ token_req,
@@ -90,23 +156,33 @@ __global__ void conv_state_update_kernel(const T* in, int ldi, int taps, int C, 
 }
 
 template <typename T>
-static int conv_launch(const void* in, int ldi, const float* w, const float* bias, int taps, int C, float* state,
+static int conv_launch(const void* in, int ldi, const float* w, const float* wt, const float* bias, int taps, int C, float* state,
                        const int* slots, const int* positions, const int* token_req, const int* req_first_token,
                        const int* req_first_position, void* out, int ldo, int n_tokens, int n_requests,
                        cudaStream_t stream) {
   const int threads = 128;
-  launch_pdl(conv_silu_kernel<T>, dim3((C + threads - 1) / threads, n_tokens), dim3(threads), 0, stream, (const T*)in,
-             ldi, w, bias, taps, C, (const float*)state, slots, positions, token_req, req_first_position, (T*)out, ldo);
+  constexpr int VEC = 16 / (int)sizeof(T);
+  const bool vec = wt != nullptr && C % VEC == 0 && ldi % VEC == 0 && ldo % VEC == 0 && C % 4 == 0 &&
+                   (((uintptr_t)in | (uintptr_t)out | (uintptr_t)state | (uintptr_t)wt) & 15) == 0;
+  if (vec) {
+    const int tv = C / VEC >= 128 ? 128 : 64;
+    launch_pdl(conv_silu_vec_kernel<T>, dim3((C / VEC + tv - 1) / tv, n_tokens), dim3(tv), 0, stream, (const T*)in, ldi,
+               wt, bias, taps, C, (const float*)state, slots, positions, token_req, req_first_position, (T*)out, ldo);
+  } else {
+    launch_pdl(conv_silu_kernel<T>, dim3((C + threads - 1) / threads, n_tokens), dim3(threads), 0, stream, (const T*)in,
+               ldi, w, bias, taps, C, (const float*)state, slots, positions, token_req, req_first_position, (T*)out, ldo);
+  }
   if (int e = mlxb_check_launch("conv_silu")) return e;
   launch_pdl(conv_state_update_kernel<T>, dim3((C + threads - 1) / threads, n_requests), dim3(threads), 0, stream,
              (const T*)in, ldi, taps, C, state, slots, token_req, req_first_token);
   return mlxb_check_launch("conv_state_update");
 }
 
-// in: [n_tokens, >= C] at row stride ldi (activation dtype); w: float32 [C, taps]; bias: float32 [C] or null;
+// in: [n_tokens, >= C] at row stride ldi (activation dtype); w: float32 [C, taps]; wt: the same tap by tap, float32
+// [taps, C], or null (with it, and sizes that allow 16-byte accesses, the vector kernel runs); bias: float32 [C] or null;
 // state: float32 [slots, taps-1, C]; out: [n_tokens, C] at row stride ldo.  Two launches: the convolution, then the
 // state's update (which must not overtake the convolution's reads of the state).
-MLXB_EXPORT int mlxb_conv_silu(int dtype, const void* in, int ldi, const float* w, const float* bias, int taps, int C,
+MLXB_EXPORT int mlxb_conv_silu(int dtype, const void* in, int ldi, const float* w, const float* wt, const float* bias, int taps, int C,
                                float* state, const int* slots, const int* positions, const int* token_req,
                                const int* req_first_token, const int* req_first_position, void* out, int ldo,
                                int n_tokens, int n_requests, cudaStream_t stream) {
@@ -116,10 +192,10 @@ MLXB_EXPORT int mlxb_conv_silu(int dtype, const void* in, int ldi, const float* 
                      ldi, ldo, n_tokens, n_requests);
   if (n_tokens > 65535) return mlxb_fail(MLXB_BAD_ARG, "conv: %d tokens are too many for one call", n_tokens);
   if (dtype == MLXB_F32)
-    return conv_launch<float>(in, ldi, w, bias, taps, C, state, slots, positions, token_req, req_first_token,
+    return conv_launch<float>(in, ldi, w, wt, bias, taps, C, state, slots, positions, token_req, req_first_token,
                               req_first_position, out, ldo, n_tokens, n_requests, stream);
   if (dtype == MLXB_BF16)
-    return conv_launch<__nv_bfloat16>(in, ldi, w, bias, taps, C, state, slots, positions, token_req, req_first_token,
+    return conv_launch<__nv_bfloat16>(in, ldi, w, wt, bias, taps, C, state, slots, positions, token_req, req_first_token,
                                       req_first_position, out, ldo, n_tokens, n_requests, stream);
   return mlxb_fail(MLXB_BAD_DTYPE, "conv: dtype code %d", dtype);
 }
@@ -316,13 +392,12 @@ MLXB_EXPORT int mlxb_mamba2_scan(int dtype, const void* xbc, int ldx, int x_off,
                                  const void* dt_raw, int lddt, const float* dt_bias, const float* A_log,
                                  const float* Dskip, float* state, const int* slots, const int* token_req,
                                  const int* req_first_token, float* y, int ldy, int H, int G, int N, int V,
-                                 int n_requests, int n_tokens, cudaStream_t stream) {
+                                 int n_requests, cudaStream_t stream) {
   if (n_requests <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || N <= 0 || V <= 0 || N > 32 * SCAN_NPT || n_requests > 65535)
     return mlxb_fail(MLXB_BAD_ARG, "mamba2_scan: %d heads in %d groups, state %d x %d (at most %d rows)", H, G, N, V,
                      32 * SCAN_NPT);
   const ScanShape sh = scan_shape(N, V, (long long)H * n_requests);
-  (void)n_tokens;
   const size_t smem = (size_t)(SCAN_CHUNK * (2 * sh.NS * SCAN_SEG + sh.VB + 2)) * sizeof(float);
   const dim3 grid(H, n_requests, sh.zblocks);
   if (dtype != MLXB_F32 && dtype != MLXB_BF16) return mlxb_fail(MLXB_BAD_DTYPE, "mamba2_scan: dtype code %d", dtype);
@@ -494,13 +569,12 @@ MLXB_EXPORT int mlxb_gated_delta_scan(int dtype, const void* qkv, int ldq, int q
                                       const void* b_raw, int ldb, const void* a_raw, int lda, const float* dt_bias,
                                       const float* A_log, float* state, const int* slots, const int* token_req,
                                       const int* req_first_token, float* o, int ldo, int H, int G, int K, int V,
-                                      int n_requests, int n_tokens, cudaStream_t stream) {
+                                      int n_requests, cudaStream_t stream) {
   if (n_requests <= 0) return 0;
   if (H <= 0 || G <= 0 || H % G || K <= 0 || V <= 0 || K > 32 * SCAN_NPT || n_requests > 65535)
     return mlxb_fail(MLXB_BAD_ARG, "gated_delta_scan: %d heads over %d key heads, state %d x %d (at most %d rows)", H, G,
                      K, V, 32 * SCAN_NPT);
   const ScanShape sh = scan_shape(K, V, (long long)H * n_requests);
-  (void)n_tokens;
   const size_t smem = (size_t)(SCAN_CHUNK * (2 * sh.NS * SCAN_SEG + sh.VB + 2)) * sizeof(float);
   const dim3 grid(H, n_requests, sh.zblocks);
   if (dtype != MLXB_F32 && dtype != MLXB_BF16) return mlxb_fail(MLXB_BAD_DTYPE, "gated_delta_scan: dtype code %d", dtype);

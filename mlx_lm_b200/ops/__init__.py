@@ -775,16 +775,18 @@ def residual_update(x, y1, stream, w1=None, y2=None, w2=None, scale: float = 1.0
 # --------------------------------------------------------------------------
 # layers with a state of fixed size per request (csrc/recurrent.cu)
 
-_CONV_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+_CONV_ARGS = [c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
               c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p]
 
 
 def conv_silu(x, weight, bias, state, slots, positions, token_req, req_first_token, req_first_position, out,
-              stream) -> None:
+              stream, weight_by_tap=None) -> None:
     """Causal convolution over time per channel, then silu: ``out[t, c] = silu(bias[c] + sum_j weight[c, taps-1-j]
     * x(t - j, c))``.  ``x``: ``[T, C]`` view (contiguous rows); ``weight`` float32 ``[C, taps]`` (last column: the
     current token); ``state`` float32 ``[slots, taps-1, C]``: each request's last inputs, read for the rows that
-    reach back before the step and brought up to date afterwards (two launches)."""
+    reach back before the step and brought up to date afterwards (two launches).  ``weight_by_tap``: the same
+    weights as float32 ``[taps, C]`` (a copy the caller keeps); with it, and with sizes that allow 16-byte accesses,
+    a thread takes eight (float32: four) neighbouring channels."""
     _need(x, out.dtype, "conv x")
     _need(weight, torch.float32, "conv weight")
     _need(state, torch.float32, "conv state")
@@ -796,13 +798,17 @@ def conv_silu(x, weight, bias, state, slots, positions, token_req, req_first_tok
                           f"out {tuple(out.shape)}")
     if bias is not None:
         _need(bias, torch.float32, "conv bias")
+    if weight_by_tap is not None:
+        _need(weight_by_tap, torch.float32, "conv weight_by_tap")
+        if weight_by_tap.shape != (taps, C) or not weight_by_tap.is_contiguous():
+            raise KernelError(f"conv: weights by tap {tuple(weight_by_tap.shape)} for {taps} taps of {C} channels")
     _call("recurrent", "mlxb_conv_silu", _CONV_ARGS, dtype_code(out.dtype), _p(x), _rows(x, "conv x"), _p(weight),
-          _p(bias), taps, C, _p(state), _p(slots), _p(positions), _p(token_req), _p(req_first_token),
+          _p(weight_by_tap), _p(bias), taps, C, _p(state), _p(slots), _p(positions), _p(token_req), _p(req_first_token),
           _p(req_first_position), _p(out), _rows(out, "conv out"), T, slots.numel(), stream)
 
 
 _M2_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
 
 
 def mamba2_scan(xbc, x_off: int, b_off: int, c_off: int, dt_raw, dt_bias, a_log, d_skip, state, slots, token_req,
@@ -822,11 +828,11 @@ def mamba2_scan(xbc, x_off: int, b_off: int, c_off: int, dt_raw, dt_bias, a_log,
     _call("recurrent", "mlxb_mamba2_scan", _M2_ARGS, dtype_code(xbc.dtype), _p(xbc), _rows(xbc, "mamba2_scan xbc"), x_off,
           b_off, c_off, _p(dt_raw), _rows(dt_raw, "mamba2_scan dt"), _p(dt_bias), _p(a_log), _p(d_skip), _p(state),
           _p(slots), _p(token_req), _p(req_first_token), _p(y), _rows(y, "mamba2_scan y"), H, n_groups, N, V,
-          slots.numel(), y.shape[0], stream)
+          slots.numel(), stream)
 
 
 _GD_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p,
-            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
+            c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p]
 
 
 def gated_delta_scan(qkv, q_off: int, k_off: int, v_off: int, b_raw, a_raw, dt_bias, a_log, state, slots, token_req,
@@ -845,7 +851,7 @@ def gated_delta_scan(qkv, q_off: int, k_off: int, v_off: int, b_raw, a_raw, dt_b
     _call("recurrent", "mlxb_gated_delta_scan", _GD_ARGS, dtype_code(qkv.dtype), _p(qkv), _rows(qkv, "gated_delta qkv"),
           q_off, k_off, v_off, _p(b_raw), _rows(b_raw, "gated_delta b"), _p(a_raw), _rows(a_raw, "gated_delta a"),
           _p(dt_bias), _p(a_log), _p(state), _p(slots), _p(token_req), _p(req_first_token), _p(o),
-          _rows(o, "gated_delta o"), H, n_key_heads, K, V, slots.numel(), o.shape[0], stream)
+          _rows(o, "gated_delta o"), H, n_key_heads, K, V, slots.numel(), stream)
 
 
 # --------------------------------------------------------------------------

@@ -59,6 +59,7 @@ class Mamba2Mixer(Mixer):
     def bind(self, tensors, dtype, device) -> None:
         n = self.name
         self.conv_w, self.conv_b = tensors[f"{n}.conv"], tensors[f"{n}.conv.b"]
+        self.conv_wt = self.conv_w.t().contiguous()      # tap by tap, for the kernel that takes eight channels a thread
         self.dt_bias, self.a_log, self.d_skip = tensors[f"{n}.dt_bias"], tensors[f"{n}.A_log"], tensors[f"{n}.D"]
         self.norm_w = tensors[f"{n}.norm"]
 
@@ -71,7 +72,7 @@ class Mamba2Mixer(Mixer):
         ops.label(self.name + ".conv", 2.0 * self.taps * T * self.conv_width, 2.0 * x.element_size() * T * self.conv_width)
         ops.conv_silu(proj[:, inner:inner + self.conv_width], self.conv_w, self.conv_b, conv_state.state,
                       conv_state.slots, ctx.positions, ctx.token_req, ctx.req_first_token, ctx.req_first_position, xbc,
-                      ctx.stream)
+                      ctx.stream, weight_by_tap=self.conv_wt)
         y = ctx.ws.get("ssm_y", T, inner, torch.float32)
         # what it has to move: its inputs and outputs, and every live request's state in and out
         ops.label(self.name + ".scan", 6.0 * T * inner * self.state, x.element_size() * T * self.conv_width + 4.0 * T * inner
@@ -134,6 +135,7 @@ class GatedDeltaMixer(Mixer):
     def bind(self, tensors, dtype, device) -> None:
         n = self.name
         self.conv_w = torch.cat([tensors[f"{n}.q.conv"], tensors[f"{n}.k.conv"], tensors[f"{n}.v.conv"]], dim=0).contiguous()
+        self.conv_wt = self.conv_w.t().contiguous()
         self.a_log, self.dt_bias, self.norm_w = tensors[f"{n}.A_log"], tensors[f"{n}.dt_bias"], tensors[f"{n}.norm"]
 
     def _gated(self, ctx, x, cache):
@@ -145,7 +147,8 @@ class GatedDeltaMixer(Mixer):
         qkv = ctx.ws.get("delta_conv", T, self.conv_width, x.dtype)
         ops.label(self.name + ".conv", 2.0 * self.taps * T * self.conv_width, 2.0 * x.element_size() * T * self.conv_width)
         ops.conv_silu(proj[:, :self.conv_width], self.conv_w, None, conv_state.state, conv_state.slots, ctx.positions,
-                      ctx.token_req, ctx.req_first_token, ctx.req_first_position, qkv, ctx.stream)
+                      ctx.token_req, ctx.req_first_token, ctx.req_first_position, qkv, ctx.stream,
+                      weight_by_tap=self.conv_wt)
         g_off = self.conv_width
         b_off = g_off + self.v_width
         o = ctx.ws.get("delta_o", T, self.v_width, torch.float32)

@@ -31,9 +31,10 @@ def run_in_steps(n_total, cuts, fn):
         lo, i = hi, i + 1
 
 
+@pytest.mark.parametrize("by_tap", [False, True])
 @pytest.mark.parametrize("act", ACT)
-@pytest.mark.parametrize("taps,C", [(4, 40), (2, 7), (3, 130)])
-def test_short_convolution_carries_its_tail(act, taps, C):
+@pytest.mark.parametrize("taps,C", [(4, 40), (2, 7), (3, 130), (4, 256)])
+def test_short_convolution_carries_its_tail(act, taps, C, by_tap):
     from mlx_lm_b200 import ops
     torch.manual_seed(taps * C)
     T = 45
@@ -50,7 +51,8 @@ def test_short_convolution_carries_its_tail(act, taps, C):
         token_req, positions, first_token, first_pos = step_arrays([n, n], [lo, lo])
         xin = torch.cat([xd[0, lo:hi], xd[1, lo:hi]]).contiguous()
         out = torch.empty(2 * n, C, dtype=act, device=DEV)
-        ops.conv_silu(xin, wd, bd, state, slots, positions, token_req, first_token, first_pos, out, ops.current_stream())
+        ops.conv_silu(xin, wd, bd, state, slots, positions, token_req, first_token, first_pos, out, ops.current_stream(),
+                      weight_by_tap=wd.t().contiguous() if by_tap else None)
         got[0, lo:hi], got[1, lo:hi] = out[:n], out[n:]
     run_in_steps(T, (1, 2, 1, 5, 3, 1, 17), step)
     tol = 1e-5 if act == torch.float32 else 2e-2
