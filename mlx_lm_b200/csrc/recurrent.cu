@@ -162,7 +162,9 @@ static int conv_launch(const void* in, int ldi, const float* w, const float* wt,
                        cudaStream_t stream) {
   const int threads = 128;
   constexpr int VEC = 16 / (int)sizeof(T);
-  const bool vec = wt != nullptr && C % VEC == 0 && ldi % VEC == 0 && ldo % VEC == 0 && C % 4 == 0 &&
+  // (with few rows the launch is a matter of latency, and more, lighter threads are the quicker: decode steps of
+  // up to 31 rows keep one channel a thread; the results are the same bits either way)
+  const bool vec = wt != nullptr && n_tokens >= 32 && C % VEC == 0 && ldi % VEC == 0 && ldo % VEC == 0 && C % 4 == 0 &&
                    (((uintptr_t)in | (uintptr_t)out | (uintptr_t)state | (uintptr_t)wt) & 15) == 0;
   if (vec) {
     const int tv = C / VEC >= 128 ? 128 : 64;
