@@ -164,7 +164,11 @@ class CacheManager:
             shape = (len(g.cache_ids), n_pages, g.spec.n_kv_heads, self.page_size, g.spec.head_dim)
             # zeros, not empty: a masked key's value row is multiplied by a zero weight and must be finite
             g.k = torch.zeros(shape, dtype=self.dtype, device=self.device)
-            g.v = torch.zeros(shape, dtype=self.dtype, device=self.device)
+            if g.spec.value_dim == 0:
+                g.v = g.k        # values are read out of the key rows
+            else:
+                g.v = torch.zeros(shape[:-1] + (g.spec.value_dim or g.spec.head_dim,), dtype=self.dtype,
+                                  device=self.device)
         for g in self.state_groups:
             shape = (len(g.cache_ids), self.max_requests) + tuple(g.spec.shape)
             g.data = torch.zeros(shape, dtype=torch.float32, device=self.device)
@@ -173,7 +177,9 @@ class CacheManager:
         n = 0
         for g in self.kv_groups:
             if g.k is not None:
-                n += 2 * g.k.numel() * g.k.element_size()
+                n += g.k.numel() * g.k.element_size()
+                if g.v is not g.k:
+                    n += g.v.numel() * g.v.element_size()
         for g in self.state_groups:
             if g.data is not None:
                 n += g.data.numel() * 4
@@ -207,9 +213,11 @@ class CacheManager:
 
     def _window_floor(self, spec: PagedKVSpec, length: int) -> int:
         """First logical page a request of ``length`` committed tokens still needs."""
-        if spec.window is None:
-            return 0
-        first_key = max(0, length - spec.window + 1)
+        first_key = 0
+        if spec.window is not None:
+            first_key = max(0, length - spec.window + 1)
+        if spec.chunk:
+            first_key = max(first_key, length // spec.chunk * spec.chunk)
         return first_key // self.page_size
 
     def pages_needed(self, rid: Hashable, n: int) -> List[int]:
@@ -253,7 +261,7 @@ class CacheManager:
         r.length += r.reserved
         r.reserved = 0
         for gi, g in enumerate(self.kv_groups):
-            if g.spec.window is None:
+            if g.spec.window is None and not g.spec.chunk:
                 continue
             floor = min(self._window_floor(g.spec, r.length), len(r.pages[gi]))
             for lp in range(floor):

@@ -13,7 +13,8 @@
 #define MLXB_ACTIVATION_LIST(X) \
   X(NONE, 0, none)              \
   X(GELU_NEW, 1, gelu_new)      \
-  X(RELU, 2, relu)
+  X(RELU, 2, relu)              \
+  X(TANH, 3, tanh)
 
 #define MLXB_EPI_ENUM(ID, CODE, NAME) EPI_##ID = CODE,
 enum { MLXB_ACTIVATION_LIST(MLXB_EPI_ENUM) };
@@ -28,6 +29,7 @@ template <int EPI, bool FAST>
 __device__ __forceinline__ float activate(float v) {
   if (EPI == EPI_GELU_NEW) return FAST ? gelu_new_fast(v) : gelu_new_f(v);
   if (EPI == EPI_RELU) return fmaxf(v, 0.f);
+  if (EPI == EPI_TANH) return tanhf(v);
   return v;
 }
 

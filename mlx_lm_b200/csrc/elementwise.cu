@@ -2,6 +2,8 @@
 //   gated_unit      out[t, j] = act(in[t, j]) * in[t, F + j]: the two halves of a fused [gate | up] projection
 //                   (act: silu = z * sigmoid(z)); float32 arithmetic, rounded once.
 //   scale_by_rows   out[t, j] = in[t, j] * table[index[t], first + j]: a per-token vector looked up in a table.
+//   xielu           out[t, j] = f(in[t, j]) with two learned numbers (a, b) of the layer, read from device memory:
+//                   z > 0: softplus(a) z^2 + z/2;  z <= 0: (1/2 + softplus(b)) (exp(z) - 1 - z) + z/2.  In place if out = in.
 //   join_rows       out[t] = [a[t] | b[t]] in the activation dtype from float32 rows (b may be null: a plain cast).
 #include "common.cuh"
 
@@ -147,4 +149,59 @@ MLXB_EXPORT int mlxb_join_rows(int dtype, const float* a, const float* b, int D,
   else
     return mlxb_fail(MLXB_BAD_DTYPE, "join_rows: dtype code %d", dtype);
   return mlxb_check_launch("join_rows");
+}
+
+__device__ __forceinline__ float softplus_f(float v) { return v > 20.f ? v : log1pf(expf(v)); }
+
+template <typename T>
+__global__ void xielu_kernel(const T* in, int ldi, T* out, int ldo, int F, int n, const float* __restrict__ act) {
+  const float ap = softplus_f(act[0]), aq = 0.5f + softplus_f(act[1]);
+  pdl_wait();
+  pdl_trigger();
+  in = after_wait(in);
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * F) return;
+  const int t = (int)(idx / F), j = (int)(idx - (long long)t * F);
+  const float z = to_f(in[(size_t)t * ldi + j]);
+  const float y = z > 0.f ? fmaf(ap * z, z, 0.5f * z) : fmaf(aq, expm1f(z) - z, 0.5f * z);
+  out[(size_t)t * ldo + j] = from_f<T>(y);
+}
+
+// Eight elements a thread (bfloat16 rows whose width, strides and bases allow 16-byte accesses).
+__global__ void xielu_bf16x8_kernel(const __nv_bfloat16* in, int ldi, __nv_bfloat16* out, int ldo, int F, int n,
+                                    const float* __restrict__ act) {
+  const float ap = softplus_f(act[0]), aq = 0.5f + softplus_f(act[1]);
+  pdl_wait();
+  pdl_trigger();
+  in = after_wait(in);
+  const int per_row = F / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= (long long)n * per_row) return;
+  const int t = (int)(idx / per_row), j = (int)(idx - (long long)t * per_row) * 8;
+  float z[8], y[8];
+  unpack8(*reinterpret_cast<const uint4*>(in + (size_t)t * ldi + j), z);
+#pragma unroll
+  for (int e = 0; e < 8; ++e) y[e] = z[e] > 0.f ? fmaf(ap * z[e], z[e], 0.5f * z[e]) : fmaf(aq, expm1f(z[e]) - z[e], 0.5f * z[e]);
+  *reinterpret_cast<uint4*>(out + (size_t)t * ldo + j) = pack8(y);
+}
+
+// act: float32 [2] on the device, the layer's two numbers before their softplus.
+MLXB_EXPORT int mlxb_xielu(int dtype, const void* in, int ldi, void* out, int ldo, int F, int n_rows, const float* act,
+                           cudaStream_t stream) {
+  if (n_rows <= 0) return 0;
+  if (F <= 0 || ldi < F || ldo < F || !act) return mlxb_fail(MLXB_BAD_ARG, "xielu: %d columns, strides %d / %d", F, ldi, ldo);
+  const long long total = (long long)n_rows * F;
+  const int threads = 256;
+  const dim3 grid((unsigned)((total + threads - 1) / threads));
+  if (dtype == MLXB_F32)
+    launch_pdl(xielu_kernel<float>, grid, dim3(threads), 0, stream, (const float*)in, ldi, (float*)out, ldo, F, n_rows, act);
+  else if (dtype == MLXB_BF16 && F % 8 == 0 && ldi % 8 == 0 && ldo % 8 == 0 && (((uintptr_t)in | (uintptr_t)out) & 15) == 0)
+    launch_pdl(xielu_bf16x8_kernel, dim3((unsigned)((total / 8 + threads - 1) / threads)), dim3(threads), 0, stream,
+               (const __nv_bfloat16*)in, ldi, (__nv_bfloat16*)out, ldo, F, n_rows, act);
+  else if (dtype == MLXB_BF16)
+    launch_pdl(xielu_kernel<__nv_bfloat16>, grid, dim3(threads), 0, stream, (const __nv_bfloat16*)in, ldi,
+               (__nv_bfloat16*)out, ldo, F, n_rows, act);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "xielu: dtype code %d", dtype);
+  return mlxb_check_launch("xielu");
 }

@@ -1,0 +1,181 @@
+// Attention over a cache of latent rows (keys and values of all heads compressed into one short vector per
+// token): what stands around the attention kernel.
+//
+// latent_prepare  From a fused projection of a token, [q | down]: `down` holds R latent columns and dr columns of a
+//                 rotated key part that all heads share.  The latent columns are divided by their root mean square
+//                 and multiplied by a weight (c); the key part is rotated by the position; [c | rotated part | 0..]
+//                 becomes the token's row in the pages (one "head", Dh >= R + dr wide).  Of every query head
+//                 ([d unrotated | dr rotated] in the projection) the rotated part is rotated the same way and put,
+//                 in float32, behind the R columns that head_linear fills: q_lat[t, h] = [W_uk_h^T q_h | rotated q].
+//                 Pairs of a rotation: (2i, 2i+1) (`interleaved`) or (i, i + dr/2); angle p * freq[i], float32.
+// head_linear     out[t, h, n] = sum_k x[t, h, k] * w[h, n, k]: a product per head, each head with its own matrix.
+//                 Absorbs the keys' up-projection into the queries (q_h -> W_uk_h^T q_h, so that scores are taken
+//                 against the latent rows directly) and applies the values' up-projection to the attention's output
+//                 over latent rows.  float32 accumulation in a fixed order (k ascending); x and out may be float32
+//                 beside bfloat16 weights, so that nothing is rounded between the attention and these products.
+#include "common.cuh"
+
+MLXB_DEFINE_LAST_ERROR()
+
+template <typename T>
+__global__ void latent_prepare_kernel(const T* proj, int ld, int q_off, int c_off, int H, int d, int dr, int R,
+                                      const float* __restrict__ w, float eps, const float* __restrict__ freq,
+                                      int interleaved, const int* __restrict__ positions,
+                                      const int* __restrict__ token_req, const int* __restrict__ block_table,
+                                      int max_pages, int n_pages, int page, int Dh, T* __restrict__ pool, int write,
+                                      float* __restrict__ q_lat, int ldq, int qhs, int* __restrict__ status) {
+  __shared__ float red[33];
+  const int t = blockIdx.x;
+  const int r = token_req[t];
+  if (r < 0) return;
+  const int p = positions[t];
+  long long slot = -1;
+  if (write) {
+    const int lp = p / page;
+    if (p < 0 || lp >= max_pages) {
+      if (threadIdx.x == 0) atomicOr(status, MLXB_ST_POSITION_RANGE);
+    } else {
+      const int pg = block_table[(size_t)r * max_pages + lp];
+      if (pg >= n_pages) {
+        if (threadIdx.x == 0) atomicOr(status, MLXB_ST_PAGE_RANGE);
+      } else if (pg >= 0) {
+        slot = ((long long)pg * page + (p % page)) * Dh;
+      }
+    }
+  }
+  pdl_wait();
+  pdl_trigger();
+  proj = after_wait(proj);
+  const T* row = proj + (size_t)t * ld;
+  const int half = dr / 2;
+  const float fp = (float)p;
+  // rotated parts: H query heads, then the shared key part
+  for (int e = threadIdx.x; e < (H + 1) * half; e += blockDim.x) {
+    const int hh = e / half, i = e - hh * half;
+    const int lo = interleaved ? 2 * i : i, hi = interleaved ? 2 * i + 1 : i + half;
+    const T* src = hh < H ? row + q_off + (size_t)hh * (d + dr) + d : row + c_off + R;
+    const float u = to_f(src[lo]), v = to_f(src[hi]);
+    float sn, cs;
+    sincosf(fp * freq[i], &sn, &cs);
+    const float a = u * cs - v * sn, b = v * cs + u * sn;
+    if (hh < H) {
+      float* dst = q_lat + (size_t)t * ldq + (size_t)hh * qhs + R;
+      dst[lo] = a;
+      dst[hi] = b;
+    } else if (slot >= 0) {
+      pool[slot + R + lo] = from_f<T>(a);
+      pool[slot + R + hi] = from_f<T>(b);
+    }
+  }
+  if (slot < 0) return;
+  float s = 0.f;
+  for (int e = threadIdx.x; e < R; e += blockDim.x) { const float v = to_f(row[c_off + e]); s = fmaf(v, v, s); }
+  const float rinv = 1.f / sqrtf(block_sum(s, red) / (float)R + eps);
+  for (int e = threadIdx.x; e < R; e += blockDim.x) pool[slot + e] = from_f<T>(to_f(row[c_off + e]) * rinv * w[e]);
+  for (int e = R + dr + threadIdx.x; e < Dh; e += blockDim.x) pool[slot + e] = from_f<T>(0.f);
+}
+
+MLXB_EXPORT int mlxb_latent_prepare(int dtype, const void* proj, int ld, int q_off, int c_off, int H, int d, int dr, int R,
+                                    const float* w, float eps, const float* freq, int interleaved, const int* positions,
+                                    const int* token_req, const int* block_table, int max_pages, int n_pages, int page,
+                                    int Dh, void* pool, int write, float* q_lat, int ldq, int qhs, int n_tokens,
+                                    int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return 0;
+  if (H <= 0 || d < 0 || dr < 0 || dr % 2 || R <= 0 || Dh < R + dr || qhs < R + dr || page <= 0 || (dr > 0 && !freq))
+    return mlxb_fail(MLXB_BAD_ARG, "latent_prepare: %d heads of %d + %d, %d latent columns in rows of %d", H, d, dr, R, Dh);
+  const int threads = R >= 512 ? 256 : 128;
+  if (dtype == MLXB_F32)
+    launch_pdl(latent_prepare_kernel<float>, dim3(n_tokens), dim3(threads), 0, stream, (const float*)proj, ld, q_off,
+               c_off, H, d, dr, R, w, eps, freq, interleaved, positions, token_req, block_table, max_pages, n_pages, page,
+               Dh, (float*)pool, write, q_lat, ldq, qhs, status);
+  else if (dtype == MLXB_BF16)
+    launch_pdl(latent_prepare_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, stream,
+               (const __nv_bfloat16*)proj, ld, q_off, c_off, H, d, dr, R, w, eps, freq, interleaved, positions, token_req,
+               block_table, max_pages, n_pages, page, Dh, (__nv_bfloat16*)pool, write, q_lat, ldq, qhs, status);
+  else
+    return mlxb_fail(MLXB_BAD_DTYPE, "latent_prepare: dtype code %d", dtype);
+  return mlxb_check_launch("latent_prepare");
+}
+
+// ---------------------------------------------------------------- a product per head
+
+constexpr int HL_TM = 64, HL_TN = 64, HL_TK = 16;
+
+// Tile of 64 tokens x 64 outputs of one head, 256 threads with 4 x 4 results each; x and w go through shared
+// memory 16 columns of k at a time.  Every result adds its k in ascending order.
+template <typename TX, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+head_linear_kernel(const TX* x, int ldx, int xhs, const TW* __restrict__ w, TO* __restrict__ out, int ldo, int ohs,
+                   int M, int N, int K, const int* __restrict__ token_req) {
+  __shared__ float sx[HL_TK][HL_TM + 4];
+  __shared__ float sw[HL_TK][HL_TN + 4];
+  const int h = blockIdx.z, m0 = blockIdx.y * HL_TM, n0 = blockIdx.x * HL_TN;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+  pdl_wait();
+  pdl_trigger();
+  x = after_wait(x);
+  const TX* xh = x + (size_t)h * xhs;
+  const TW* wh = w + (size_t)h * N * K;
+  float acc[4][4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) acc[i][j] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += HL_TK) {
+    __syncthreads();
+    for (int e = tid; e < HL_TM * HL_TK; e += 256) {
+      const int mm = e / HL_TK, kk = e - mm * HL_TK;
+      const int m = m0 + mm, k = k0 + kk;
+      sx[kk][mm] = (m < M && k < K) ? to_f(xh[(size_t)m * ldx + k]) : 0.f;
+    }
+    for (int e = tid; e < HL_TN * HL_TK; e += 256) {
+      const int nn = e / HL_TK, kk = e - nn * HL_TK;
+      const int n = n0 + nn, k = k0 + kk;
+      sw[kk][nn] = (n < N && k < K) ? to_f(wh[(size_t)n * K + k]) : 0.f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < HL_TK; ++kk) {
+      const float4 a = *reinterpret_cast<const float4*>(&sx[kk][ty * 4]);
+      const float4 b = *reinterpret_cast<const float4*>(&sw[kk][tx * 4]);
+      const float av[4] = {a.x, a.y, a.z, a.w}, bv[4] = {b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+#pragma unroll
+        for (int j = 0; j < 4; ++j) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int m = m0 + ty * 4 + i;
+    if (m >= M || (token_req && token_req[m] < 0)) continue;
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const int n = n0 + tx * 4 + j;
+      if (n < N) out[(size_t)m * ldo + (size_t)h * ohs + n] = from_f<TO>(acc[i][j]);
+    }
+  }
+}
+
+// x: [M, .] at row stride ldx, head h from column h*xhs (K values), float32 if x_f32 else `dtype`; w: `dtype`
+// [H, N, K]; out: [M, .] at row stride ldo, head h from column h*ohs (N values), float32 if out_f32 else `dtype`;
+// token_req: int32 [M] or null: rows whose entry is negative are not written.
+MLXB_EXPORT int mlxb_head_linear(int dtype, int x_f32, int out_f32, const void* x, int ldx, int xhs, const void* w,
+                                 void* out, int ldo, int ohs, int M, int N, int K, int H, const int* token_req,
+                                 cudaStream_t stream) {
+  if (M <= 0) return 0;
+  if (N <= 0 || K <= 0 || H <= 0 || xhs < K || ohs < N || H > 65535)
+    return mlxb_fail(MLXB_BAD_ARG, "head_linear: %d heads of %d x %d, head strides %d / %d", H, N, K, xhs, ohs);
+  const dim3 grid((N + HL_TN - 1) / HL_TN, (M + HL_TM - 1) / HL_TM, H), block(256);
+#define HL_GO(TX, TW, TO)                                                                                             \
+  launch_pdl(head_linear_kernel<TX, TW, TO>, grid, block, 0, stream, (const TX*)x, ldx, xhs, (const TW*)w, (TO*)out, \
+             ldo, ohs, M, N, K, token_req)
+  if (dtype == MLXB_F32) HL_GO(float, float, float);
+  else if (dtype != MLXB_BF16) return mlxb_fail(MLXB_BAD_DTYPE, "head_linear: dtype code %d", dtype);
+  else if (x_f32 && out_f32) HL_GO(float, __nv_bfloat16, float);
+  else if (x_f32) HL_GO(float, __nv_bfloat16, __nv_bfloat16);
+  else if (out_f32) HL_GO(__nv_bfloat16, __nv_bfloat16, float);
+  else HL_GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+#undef HL_GO
+  return mlxb_check_launch("head_linear");
+}

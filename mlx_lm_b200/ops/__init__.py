@@ -859,21 +859,25 @@ def gated_delta_scan(qkv, q_off: int, k_off: int, v_off: int, b_raw, a_raw, dt_b
 
 _QKVP_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
               c_float, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p,
-              c_void_p, c_int, c_int, c_void_p, c_void_p]
+              c_void_p, c_int, c_int, c_void_p, c_int, c_float, c_int, c_int, c_void_p]
 
 
 def qkv_prepare(proj, q_off: int, k_off: int, v_off: int, n_heads: int, n_kv_heads: int, dk: int, dv: int, q_norm,
                 k_norm, eps: float, freq, positions, token_req, block_table, k_pool, v_pool, q_out, write: bool, status,
-                stream) -> None:
+                stream, interleaved: bool = False, v_norm_eps: Optional[float] = None) -> None:
     """From a fused projection ``proj [T, .]``: optional RMS norm over a token's whole q and whole k projection
     (float32 weights ``q_norm``, ``k_norm`` or None), rotation of the first ``2 * len(freq)`` dimensions of every
     head by the token's position (pairs ``(i, i + len(freq))``; ``freq`` float32 or None), q into ``q_out
-    [T, n_heads*Dh]``, k and v into the pages ``[n_pages, n_kv_heads, page, Dh]``; columns of a head beyond
-    ``dk`` / ``dv`` are zeros."""
+    [T, n_heads*Dh]``, k and v into the pages ``[n_pages, n_kv_heads, page, Dh]`` (values: their own row width); columns of a head beyond
+    ``dk`` / ``dv`` are zeros.  ``interleaved``: the pairs are ``(2i, 2i+1)``.  ``v_norm_eps``: every value head is
+    divided by its root mean square (this eps inside the root, no weight) before it enters the page.  ``q_out`` may
+    be float32 in a bfloat16 run."""
     n_pages, Hkv, page, Dh = k_pool.shape
     _need(proj, k_pool.dtype, "qkv_prepare proj")
-    _need(q_out, k_pool.dtype, "qkv_prepare q_out")
-    if Hkv != n_kv_heads or q_out.shape[1] != n_heads * Dh or not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+    if q_out.dtype != torch.float32:
+        _need(q_out, k_pool.dtype, "qkv_prepare q_out")
+    if (Hkv != n_kv_heads or q_out.shape[1] != n_heads * Dh or not (k_pool.is_contiguous() and v_pool.is_contiguous())
+            or v_pool.shape[:3] != k_pool.shape[:3]):
         raise KernelError(f"qkv_prepare: pools {tuple(k_pool.shape)}, q_out {tuple(q_out.shape)}")
     half = 0
     if freq is not None:
@@ -887,11 +891,173 @@ def qkv_prepare(proj, q_off: int, k_off: int, v_off: int, n_heads: int, n_kv_hea
     _call("rotary", "mlxb_qkv_prepare", _QKVP_ARGS, dtype_code(k_pool.dtype), _p(proj), _rows(proj, "qkv_prepare proj"),
           q_off, k_off, v_off, n_heads, n_kv_heads, dk, dv, Dh, _p(q_norm), _p(k_norm), float(eps), _p(freq), half,
           _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, _p(q_out),
-          _rows(q_out, "qkv_prepare q_out"), _p(k_pool), _p(v_pool), int(bool(write)), proj.shape[0], _p(status), stream)
+          _rows(q_out, "qkv_prepare q_out"), _p(k_pool), _p(v_pool), int(bool(write)), proj.shape[0], _p(status),
+          int(bool(interleaved)), -1.0 if v_norm_eps is None else float(v_norm_eps),
+          int(q_out.dtype == torch.float32 and k_pool.dtype != torch.float32), v_pool.shape[3], stream)
+
+
+# --------------------------------------------------------------------------
+# attention with a whole group of heads per CTA (csrc/attention_wide.cu)
+
+_WIDE_ARGS = [c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+              c_int, c_void_p, c_int, c_void_p, c_void_p]
+
+
+def attention_wide(q, q_head_stride: int, positions, token_req, block_table, k_pool, v_pool, out, out_head_stride: int,
+                   n_heads: int, key_dim: int, value_dim: int, scale: float, status, stream, window: int = 0,
+                   chunk: int = 0, talk=None, gate=None, rows=None) -> None:
+    """Causal attention of float32 queries ``q [T, .]`` (head ``h`` from column ``h * q_head_stride``, ``key_dim``
+    values) over pages ``k_pool [n_pages, kv_heads, page, key row]`` and ``v_pool [n_pages, kv_heads, page, value
+    row]`` (``v_pool`` may be ``k_pool``: a value is then the first ``value_dim`` columns of the key row).  Position
+    ``p`` sees ``j <= p`` with ``p - j < window`` (if ``window``) and ``j // chunk == p // chunk`` (if ``chunk``).
+    ``talk``: float32 ``[n_heads, n_heads]``, the heads' scores mixed before the softmax; ``gate``: ``[T, n_heads]``
+    in the pools' dtype, head ``h``'s output times ``sigmoid(gate[t, h])``.  ``out``: the pools' dtype or float32."""
+    _need(q, torch.float32, "attention_wide q")
+    _need(k_pool, None, "attention_wide k_pool")
+    _need(v_pool, k_pool.dtype, "attention_wide v_pool")
+    n_pages, Hkv, page, krs = k_pool.shape
+    vrs = v_pool.shape[3]
+    if v_pool.shape[:3] != k_pool.shape[:3] or not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+        raise KernelError(f"attention_wide: pools {tuple(k_pool.shape)} and {tuple(v_pool.shape)}")
+    if out.dtype not in (k_pool.dtype, torch.float32) or out.shape[0] != q.shape[0]:
+        raise KernelError(f"attention_wide: out {out.dtype} {tuple(out.shape)} for q {tuple(q.shape)}")
+    if talk is not None:
+        _need(talk, torch.float32, "attention_wide talk")
+        if talk.shape != (n_heads, n_heads) or not talk.is_contiguous():
+            raise KernelError(f"attention_wide: talk {tuple(talk.shape)} for {n_heads} heads")
+    ldg = 0
+    if gate is not None:
+        _need(gate, k_pool.dtype, "attention_wide gate")
+        if gate.shape[1] != n_heads:
+            raise KernelError(f"attention_wide: gate {tuple(gate.shape)} for {n_heads} heads")
+        ldg = _rows(gate, "attention_wide gate")
+    n = q.shape[0] if rows is None else rows.numel()
+    _call("attention_wide", "mlxb_attention_wide", _WIDE_ARGS, dtype_code(k_pool.dtype), int(out.dtype == torch.float32
+          and k_pool.dtype != torch.float32), _p(q), _rows(q, "attention_wide q"), q_head_stride, _p(positions),
+          _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, key_dim, value_dim, krs, vrs,
+          int(window or 0), int(chunk or 0), float(scale), _p(talk), _p(k_pool), _p(v_pool), _p(gate), ldg, _p(out),
+          _rows(out, "attention_wide out"), out_head_stride, _p(rows), n, _p(status), stream)
+
+
+# --------------------------------------------------------------------------
+# attention over latent rows: what stands around it (csrc/latent.cu)
+
+_LATP_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_int, c_void_p,
+              c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p,
+              c_void_p]
+
+
+def latent_prepare(proj, q_off: int, c_off: int, n_heads: int, dim: int, rot_dim: int, rank: int, norm_weight, eps: float,
+                   freq, interleaved: bool, positions, token_req, block_table, pool, write: bool, q_lat,
+                   q_head_stride: int, status, stream) -> None:
+    """From ``proj [T, .]`` holding ``q`` (``n_heads`` heads of ``[dim | rot_dim]`` from ``q_off``) and the down
+    projection (``rank + rot_dim`` columns from ``c_off``): the token's latent row ``[rmsnorm(c) * weight | rotated
+    key part | 0..]`` into ``pool [n_pages, 1, page, row]``, and every head's rotated query part, float32, into
+    columns ``rank ..`` of its ``q_head_stride`` columns of ``q_lat``."""
+    n_pages, one, page, Dh = pool.shape
+    _need(proj, pool.dtype, "latent_prepare proj")
+    _need(q_lat, torch.float32, "latent_prepare q_lat")
+    _need(norm_weight, torch.float32, "latent_prepare norm weight")
+    if one != 1 or not pool.is_contiguous() or norm_weight.numel() != rank or q_lat.shape[1] < n_heads * q_head_stride:
+        raise KernelError(f"latent_prepare: pool {tuple(pool.shape)}, q_lat {tuple(q_lat.shape)}, rank {rank}")
+    if rot_dim:
+        _need(freq, torch.float32, "latent_prepare freq")
+        if freq.numel() != rot_dim // 2:
+            raise KernelError(f"latent_prepare: {freq.numel()} frequencies for {rot_dim} rotated dimensions")
+    _call("latent", "mlxb_latent_prepare", _LATP_ARGS, dtype_code(pool.dtype), _p(proj), _rows(proj, "latent_prepare proj"),
+          q_off, c_off, n_heads, dim, rot_dim, rank, _p(norm_weight), float(eps), _p(freq), int(bool(interleaved)),
+          _p(positions), _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, Dh, _p(pool),
+          int(bool(write)), _p(q_lat), _rows(q_lat, "latent_prepare q_lat"), q_head_stride, proj.shape[0], _p(status),
+          stream)
+
+
+_HEADLIN_ARGS = [c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                 c_void_p, c_void_p]
+
+
+def head_linear(x, x_head_stride: int, w, out, out_head_stride: int, stream, token_req=None) -> None:
+    """``out[t, h, n] = sum_k x[t, h, k] * w[h, n, k]``: head ``h`` of ``x [T, .]`` from column ``h * x_head_stride``,
+    of ``out`` from ``h * out_head_stride``; ``w [H, N, K]`` in the run's dtype; ``x`` and ``out`` in that dtype or
+    float32.  Rows whose ``token_req`` is negative are not written."""
+    _need(w, None, "head_linear w")
+    H, N, K = w.shape
+    for t, what in ((x, "x"), (out, "out")):
+        if t.dtype not in (w.dtype, torch.float32) or not t.is_cuda:
+            raise KernelError(f"head_linear: {what} is {t.dtype} on {t.device} for weights in {w.dtype}")
+    if not w.is_contiguous() or out.shape[0] != x.shape[0]:
+        raise KernelError(f"head_linear: w {tuple(w.shape)}, x {tuple(x.shape)}, out {tuple(out.shape)}")
+    _call("latent", "mlxb_head_linear", _HEADLIN_ARGS, dtype_code(w.dtype),
+          int(x.dtype == torch.float32 and w.dtype != torch.float32),
+          int(out.dtype == torch.float32 and w.dtype != torch.float32), _p(x), _rows(x, "head_linear x"), x_head_stride,
+          _p(w), _p(out), _rows(out, "head_linear out"), out_head_stride, x.shape[0], N, K, H, _p(token_req), stream)
+
+
+# --------------------------------------------------------------------------
+# time mixing with a data-dependent decay (csrc/wkv.cu)
+
+_SHIFT_ARGS = [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+               c_int, c_int, c_int, c_int, c_void_p]
+
+
+def token_shift_mix(x, mu, state, slots, positions, token_req, req_first_token, out, stream) -> None:
+    """``out[t, s*sec : s*sec + D] = x[t] + (prev[t] - x[t]) * mu[s]`` for every mix ``s`` (``mu`` float32 ``[n_mix, D]``;
+    ``out [T, n_mix*sec]`` with ``sec >= D``),
+    ``prev`` the row of the token before ``t`` in its request: a row of this step, or ``state[slot]`` (float32
+    ``[slots, D]``, the last row of the step before; zeros at position 0).  A second launch leaves every request's
+    last row in the state."""
+    _need(x, out.dtype, "token_shift_mix x")
+    _need(mu, torch.float32, "token_shift_mix mu")
+    _need(state, torch.float32, "token_shift_mix state")
+    T, D = x.shape
+    n_mix = mu.shape[0]
+    if mu.shape != (n_mix, D) or not mu.is_contiguous() or state.shape[1:] != (D,) or not state.is_contiguous() \
+            or out.shape[0] != T or out.shape[1] % n_mix or out.shape[1] // n_mix < D:
+        raise KernelError(f"token_shift_mix: x {tuple(x.shape)}, mu {tuple(mu.shape)}, state {tuple(state.shape)}, "
+                          f"out {tuple(out.shape)}")
+    _call("wkv", "mlxb_token_shift_mix", _SHIFT_ARGS, dtype_code(out.dtype), _p(x), _rows(x, "token_shift_mix x"), _p(mu),
+          n_mix, D, _p(state), _p(slots), _p(positions), _p(token_req), _p(req_first_token), _p(out),
+          _rows(out, "token_shift_mix out"), out.shape[1] // n_mix, T, slots.numel(), stream)
+
+
+_WKV_ARGS = [c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+             c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p]
+
+
+def wkv_scan(rkv, r_off: int, k_off: int, v_off: int, decay_raw, bonus, state, slots, token_req, req_first_token, o,
+             n_heads: int, stream) -> None:
+    """Per (request, head): ``o_t = (S + diag(u) k_t v_t^T)^T r_t``, then ``S <- diag(w_t) S + k_t v_t^T`` with
+    ``w_t = exp(-exp(decay_raw_t))``.  ``rkv [T, .]`` holds r, k, v from the given column offsets; ``decay_raw``
+    float32 ``[T, heads*K]``; ``bonus`` (u) float32 ``[heads, K]``; ``state`` float32 ``[slots, heads, V, K]`` (a head's
+    ``K x V`` state column by column); ``o`` float32 ``[T, heads*V]``."""
+    _need(state, torch.float32, "wkv_scan state")
+    _need(o, torch.float32, "wkv_scan o")
+    _need(decay_raw, torch.float32, "wkv_scan decay")
+    _need(bonus, torch.float32, "wkv_scan bonus")
+    _, H, V, K = state.shape
+    if H != n_heads or o.shape[1] != H * V or not state.is_contiguous() or bonus.numel() != H * K \
+            or not bonus.is_contiguous() or decay_raw.shape[1] != H * K:
+        raise KernelError(f"wkv_scan: state {tuple(state.shape)} for {n_heads} heads, o {tuple(o.shape)}, "
+                          f"decay {tuple(decay_raw.shape)}, bonus {tuple(bonus.shape)}")
+    _call("wkv", "mlxb_wkv_scan", _WKV_ARGS, dtype_code(rkv.dtype), _p(rkv), _rows(rkv, "wkv_scan rkv"), r_off, k_off,
+          v_off, _p(decay_raw), _rows(decay_raw, "wkv_scan decay"), _p(bonus), _p(state), _p(slots), _p(token_req),
+          _p(req_first_token), _p(o), _rows(o, "wkv_scan o"), H, K, V, slots.numel(), stream)
 
 
 # --------------------------------------------------------------------------
 # small row-wise kernels (csrc/elementwise.cu)
+
+def xielu(x, out, params, stream) -> None:
+    """``out = f(x)`` elementwise (``out`` may be ``x``) with the layer's two numbers ``params`` (float32 ``[2]`` on
+    the device): ``z > 0: softplus(a) z^2 + z/2``; ``z <= 0: (1/2 + softplus(b)) (exp(z) - 1 - z) + z/2``."""
+    _need(x, out.dtype, "xielu x")
+    _need(params, torch.float32, "xielu params")
+    T, F_ = out.shape
+    if x.shape != out.shape or params.numel() != 2:
+        raise KernelError(f"xielu: x {tuple(x.shape)}, out {tuple(out.shape)}, {params.numel()} parameters")
+    _call("elementwise", "mlxb_xielu", [c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+          dtype_code(out.dtype), _p(x), _rows(x, "xielu x"), _p(out), _rows(out, "xielu out"), F_, T, _p(params), stream)
+
 
 def gated_unit(x, out, stream) -> None:
     """``out[t, j] = silu(x[t, j]) * x[t, F + j]`` for ``x [T, 2F]``: the halves of a fused [gate | up] projection."""

@@ -1,12 +1,12 @@
 from .base import (INT_TABLE, MATRIX, VECTOR, Block, FeedForward, Init, Mixer, Norm, PagedKVSpec, ParamSpec, Part,
                    PositionEncoding, StateSpec, make_part, register_part, registered_parts)
 from .block import PreNormBlock, StreamBlock
-from .feed_forward import MLP, GatedMLP
+from .feed_forward import MLP, GatedMLP, LearnedActMLP
 from .linear import FusedLinear, Linear
-from .mixers import Attention, ParallelMixer, SinkAttention
+from .mixers import Attention, LatentAttention, ParallelMixer, SinkAttention, TalkingHeadsAttention
 from .model import LoopInput, Model, ModelDescription, OutputHead, Reentry, RunEntry, TokenEmbedding
 from .norms import LayerNorm, RMSNorm
-from .recurrent import GatedDeltaMixer, Mamba2Mixer
+from .recurrent import GatedDeltaMixer, Mamba2Mixer, WKVMixer
 from .side import TokenSideInput
 from .positions import LearnedAbsolute, NoPosition
 
@@ -15,4 +15,4 @@ __all__ = ["INT_TABLE", "MATRIX", "VECTOR", "Block", "FeedForward", "Init", "Mix
            "PreNormBlock", "MLP", "Linear", "Attention", "Model", "ModelDescription", "OutputHead", "RunEntry",
            "TokenEmbedding", "LayerNorm", "LearnedAbsolute", "NoPosition", "StreamBlock", "GatedMLP", "FusedLinear",
            "ParallelMixer", "SinkAttention", "LoopInput", "Reentry", "RMSNorm", "GatedDeltaMixer", "Mamba2Mixer",
-           "TokenSideInput"]
+           "TokenSideInput", "LearnedActMLP", "LatentAttention", "TalkingHeadsAttention", "WKVMixer"]

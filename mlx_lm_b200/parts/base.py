@@ -52,10 +52,15 @@ class ParamSpec:
 
 @dataclass(frozen=True)
 class PagedKVSpec:
-    """Keys and values of every position (``window=None``) or of the last ``window`` positions."""
+    """Keys and values of every position (``window=None``) or of the last ``window`` positions.  ``chunk``: a
+    position reads only keys of its own run of ``chunk`` positions (runs counted from position 0), so pages that
+    lie wholly before the current run are given back.  ``value_dim``: width of a value row if it differs from
+    ``head_dim``; 0: no value pool at all, values are read out of the key rows (a cache of latent rows)."""
     n_kv_heads: int
     head_dim: int
     window: Optional[int] = None
+    chunk: Optional[int] = None
+    value_dim: Optional[int] = None
 
 
 @dataclass(frozen=True)

@@ -5,7 +5,7 @@ epilogue and the residual add in the second's."""
 
 from __future__ import annotations
 
-from .base import FeedForward, Init, register_part
+from .base import VECTOR, FeedForward, Init, ParamSpec, register_part
 import torch
 
 from .. import ops
@@ -65,3 +65,42 @@ class GatedMLP(FeedForward):
 
 
 register_part("feed_forward", "gated_mlp", GatedMLP)
+
+
+class LearnedActMLP(FeedForward):
+    """``down(act(up(x)))`` without biases, where ``act`` has numbers of its own that the layer learns (a tensor
+    ``<name>.act``).  ``xielu``: two numbers ``(a, b)``; ``z > 0: softplus(a) z^2 + z/2``,
+    ``z <= 0: (1/2 + softplus(b)) (exp(z) - 1 - z) + z/2``.  The activation is a kernel of its own between the two
+    products (float32 arithmetic, in place); the residual stream (float32) is added in the second product's epilogue."""
+    replayable = True
+    kernel_libs = ("elementwise",)
+    ACTS = {"xielu": 2}      # name -> how many numbers
+
+    def __init__(self, name: str, width: int, inner: int, activation: str = "xielu", up_name: str = "up",
+                 down_name: str = "down", act_name: str = "act", init: Init = Init()):
+        if activation not in self.ACTS:
+            raise ValueError(f"{name}: activation {activation!r} is not one of {sorted(self.ACTS)}")
+        self.name, self.width, self.inner, self.activation = name, width, inner, activation
+        self.act_name = f"{name}.{act_name}"
+        self.up = Linear(f"{name}.{up_name}", width, inner, bias=False, weight_suffix="", init=init)
+        self.down = Linear(f"{name}.{down_name}", inner, width, bias=False, weight_suffix="", init=Init(0.0, inner ** -0.5))
+        self.act = None
+
+    def children(self):
+        return (self.up, self.down)
+
+    def param_specs(self):
+        return [ParamSpec(self.act_name, (self.ACTS[self.activation],), VECTOR, Init(0.0, 0.5))]
+
+    def bind(self, tensors, dtype, device) -> None:
+        self.act = tensors[self.act_name].contiguous()
+
+    def forward(self, ctx, x, residual):
+        T = x.shape[0]
+        h = self.up.forward(ctx, x, ctx.ws.get("ffn_hidden", T, self.inner, x.dtype))
+        ops.label(self.name + ".act", 8.0 * T * self.inner, 2.0 * x.element_size() * T * self.inner)
+        ops.xielu(h, h, self.act, ctx.stream)
+        return self.down.forward(ctx, h, residual, residual=residual)
+
+
+register_part("feed_forward", "learned_act_mlp", LearnedActMLP)

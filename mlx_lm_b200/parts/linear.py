@@ -137,12 +137,18 @@ class Linear(Part):
 class FusedLinear(Linear):
     """Several linear layers that read the same input, stored as separate ``[out, in]`` tensors and run as one
     product: the weights are stacked at bind time, the output holds the layers' results side by side in the
-    order of ``sources`` (``offset(name)`` gives a layer's first column).  No biases."""
+    order of ``sources`` (``offset(name)`` gives a layer's first column).  ``biases``: ``{weight tensor: bias
+    tensor}`` for the layers that have a bias (float32, added in the product's epilogue; the others add zero)."""
 
-    def __init__(self, name: str, n_in: int, sources, init: Init = Init(), tensor_core_from: Optional[int] = None):
+    def __init__(self, name: str, n_in: int, sources, init: Init = Init(), tensor_core_from: Optional[int] = None,
+                 biases=None, bias_init: Init = Init()):
         self.sources = [(str(n), int(k)) for n, k in sources]
+        self.bias_names = dict(biases or {})
+        unknown = set(self.bias_names) - {n for n, _ in self.sources}
+        if unknown:
+            raise ValueError(f"{name}: biases for {sorted(unknown)}, which are not among its layers")
         super().__init__(name, n_in, sum(k for _, k in self.sources), bias=False, stored="out_in", weight_suffix="",
-                         init=init, tensor_core_from=tensor_core_from)
+                         init=init, bias_init=bias_init, tensor_core_from=tensor_core_from)
 
     def offset(self, tensor_name: str) -> int:
         off = 0
@@ -153,8 +159,17 @@ class FusedLinear(Linear):
         raise KeyError(tensor_name)
 
     def param_specs(self) -> List[ParamSpec]:
-        return [ParamSpec(n, (k, self.n_in), MATRIX, self.init) for n, k in self.sources]
+        specs = []
+        for n, k in self.sources:
+            specs.append(ParamSpec(n, (k, self.n_in), MATRIX, self.init))
+            if n in self.bias_names:
+                specs.append(ParamSpec(self.bias_names[n], (k,), VECTOR, self.bias_init))
+        return specs
 
     def bind(self, tensors, dtype, device) -> None:
         self.weight = torch.cat([tensors[n] for n, _ in self.sources], dim=0).contiguous()
         self.bias = None
+        if self.bias_names:
+            self.bias = torch.cat([tensors[self.bias_names[n]].float() if n in self.bias_names
+                                   else torch.zeros(k, dtype=torch.float32, device=self.weight.device)
+                                   for n, k in self.sources]).contiguous()

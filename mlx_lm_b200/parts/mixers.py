@@ -17,7 +17,7 @@ from typing import List, Optional
 import torch
 
 from .. import ops
-from .base import VECTOR, Init, Mixer, Normed, PagedKVSpec, ParamSpec, PositionEncoding, register_part
+from .base import MATRIX, VECTOR, Init, Mixer, Normed, PagedKVSpec, ParamSpec, PositionEncoding, register_part
 from .linear import FusedLinear, Linear
 
 
@@ -253,5 +253,184 @@ class ParallelMixer(Mixer):
         return residual
 
 
+class TalkingHeadsAttention(Mixer):
+    """Grouped-query causal attention in which a CTA of the attention kernel takes all heads of a query
+    (``ops.attention_wide``), with these options, each a parameter:
+
+    * separate ``q``, ``k``, ``v`` tensors with biases ``<tensor>.b`` (``bias``), run as one product together
+      with the gate's; key/query size ``dim`` and value size ``vdim`` may differ;
+    * ``rot_dims``: the first so many dimensions of every q and k head turn with the position, angle
+      ``p * rot_base**(-2i/rot_dims)``, pairs ``(i, i + rot_dims/2)`` or, ``interleaved``, ``(2i, 2i+1)``;
+    * ``value_norm``: every value head is divided by its root mean square (eps inside the root, no weight)
+      before it enters the cache;
+    * ``talk``: the heads' scores ``scale * q_g . k`` are mixed before the softmax, ``s_h <- sum_g T[h, g] s_g``
+      with ``T`` = ``<name>.talk`` ``[heads, heads]``;
+    * ``window``: position ``p`` sees the last ``window`` positions; ``chunk``: it sees ``j <= p`` of its own run of
+      ``chunk`` positions, runs counted from position 0 of the sequence (earlier runs' pages are given back);
+    * ``head_gate``: head ``h``'s output times ``sigmoid(W_g x)_h`` (``<name>.g`` ``[heads, width]``, the mixer's own
+      input), before the output projection ``<name>.o`` (bias ``<name>.o.b``).
+
+    Queries go to the kernel in float32; scores, their mix and the softmax are float32."""
+    replayable = True
+    kernel_libs = ("attention_wide", "rotary")
+
+    def __init__(self, name: str, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
+                 eps: float, rot_dims: int = 0, rot_base: float = 10000.0, interleaved: bool = False, bias: bool = True,
+                 talk: bool = True, value_norm: bool = True, head_gate: bool = True, window: Optional[int] = None,
+                 chunk: Optional[int] = None, init: Init = Init(), bias_init: Init = Init()):
+        if n_heads % n_kv_heads:
+            raise ValueError(f"{name}: {n_heads} query heads are not a multiple of {n_kv_heads} key/value heads")
+        if rot_dims % 2 or rot_dims > dim:
+            raise ValueError(f"{name}: {rot_dims} rotated dimensions of {dim}")
+        self.name, self.width = name, width
+        self.n_heads, self.n_kv_heads, self.dim, self.vdim = n_heads, n_kv_heads, dim, vdim
+        self.key_row, self.value_row = (dim + 7) // 8 * 8, (vdim + 7) // 8 * 8     # rows of the pages: whole 16 bytes
+        self.scale, self.eps, self.window, self.chunk = float(scale), float(eps), window, chunk
+        self.rot_dims, self.rot_base, self.interleaved = rot_dims, float(rot_base), interleaved
+        self.has_talk, self.value_norm, self.head_gate = talk, value_norm, head_gate
+        sources = [(f"{name}.q", n_heads * dim), (f"{name}.k", n_kv_heads * dim), (f"{name}.v", n_kv_heads * vdim)]
+        biases = {n: n + ".b" for n, _ in sources} if bias else None
+        if head_gate:
+            sources.append((f"{name}.g", n_heads))
+        self.proj = FusedLinear(f"{name}.qkvg", width, sources, init=init, biases=biases, bias_init=bias_init)
+        self.out = Linear(f"{name}.o", n_heads * vdim, width, bias=False, weight_suffix="", init=init)
+        self.has_bias, self.bias_init = bias, bias_init
+        self.talk = self.freq = None
+
+    def children(self):
+        return (self.proj, self.out)
+
+    def cache_spec(self):
+        return PagedKVSpec(self.n_kv_heads, self.key_row, self.window, chunk=self.chunk, value_dim=self.value_row)
+
+    def param_specs(self) -> List[ParamSpec]:
+        specs = []
+        if self.has_talk:
+            specs.append(ParamSpec(f"{self.name}.talk", (self.n_heads, self.n_heads), VECTOR, Init(0.0, 0.5)))
+        if self.has_bias:
+            specs.append(ParamSpec(f"{self.name}.o.b", (self.width,), VECTOR, self.bias_init))
+        return specs
+
+    def bind(self, tensors, dtype, device) -> None:
+        if self.has_talk:
+            self.talk = tensors[f"{self.name}.talk"].contiguous()
+        if self.rot_dims:
+            i = torch.arange(self.rot_dims // 2, dtype=torch.float64)
+            self.freq = (self.rot_base ** (-2.0 * i / self.rot_dims)).to(torch.float32).to(device)
+
+    def bind_all(self, tensors, dtype, device) -> None:
+        super().bind_all(tensors, dtype, device)
+        if self.has_bias:
+            self.out.bias = tensors[f"{self.name}.o.b"]     # named beside the tensor, not ".bias": set once the layer is bound
+
+    def forward(self, ctx, x, residual, cache):
+        T, H, G = x.shape[0], self.n_heads, self.n_kv_heads
+        n = self.proj.n_out
+        proj = ctx.ws.get("attn_proj", T, (n + 7) // 8 * 8, x.dtype)[:, :n]
+        self.proj.forward(ctx, x, proj)
+        q = ctx.ws.get("attn_q32", T, H * self.key_row, torch.float32)
+        ops.label(self.name + ".prepare", 8.0 * T * n, (x.element_size() + 4.0) * T * n)
+        self._prepare(ctx, proj, cache, q)
+        o = ctx.ws.get("attn_out", T, H * self.vdim, x.dtype)
+        ops.label(self.name + ".attention")
+        g_off = (H + G) * self.dim + G * self.vdim
+        ops.attention_wide(q, self.key_row, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o, self.vdim,
+                           H, self.dim, self.vdim, self.scale, ctx.status, ctx.stream, window=self.window or 0,
+                           chunk=self.chunk or 0, talk=self.talk,
+                           gate=proj[:, g_off:g_off + H] if self.head_gate else None)
+        return self.out.forward(ctx, o, residual, residual=residual)
+
+    def _prepare(self, ctx, proj, cache, q) -> None:
+        H, G = self.n_heads, self.n_kv_heads
+        ops.qkv_prepare(proj, 0, H * self.dim, (H + G) * self.dim, H, G, self.dim, self.vdim, None, None, self.eps,
+                        self.freq, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, q, cache.write,
+                        ctx.status, ctx.stream, interleaved=self.interleaved,
+                        v_norm_eps=self.eps if self.value_norm else None)
+
+
+class LatentAttention(Mixer):
+    """Attention whose keys and values of all heads are kept as one short latent row per token.
+
+    ``<name>.q`` gives every head ``[dim unrotated | rot_dim rotated]`` query dimensions; ``<name>.dkv`` gives
+    ``kv_rank`` latent columns, RMS-normed with the weight ``<name>.dkv.norm`` (``c``), and ``rot_dim`` columns of a
+    rotated key part that all heads share.  Head ``h``'s unrotated key is ``W_uk_h c`` (``<name>.uk``) and its value
+    ``W_uv_h c`` (``<name>.uv``); its score is ``scale * (q_unrotated . k_unrotated + q_rotated . k_rotated)``.
+
+    The pages hold ``[c | rotated key part]`` only (one row per token, no value pool).  The keys' up-projection
+    is applied to the queries instead (``q_h -> W_uk_h^T q_h``, a product per head), the attention runs over the latent
+    rows with all heads sharing them (the values are the rows' first ``kv_rank`` columns), and the values'
+    up-projection is applied to its output (again a product per head), then ``<name>.o``.  Queries and the
+    attention's output stay float32 between those products.  Rotation pairs ``(2i, 2i+1)`` (``interleaved``) or
+    ``(i, i + rot_dim/2)``; ``window`` as in the other attention parts."""
+    replayable = True
+    kernel_libs = ("attention_wide", "latent")
+
+    def __init__(self, name: str, width: int, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
+                 scale: float, eps: float, rot_base: float = 10000.0, interleaved: bool = True,
+                 window: Optional[int] = None, chunk: Optional[int] = None, init: Init = Init()):
+        if rot_dim % 2:
+            raise ValueError(f"{name}: {rot_dim} rotated dimensions")
+        self.name, self.width = name, width
+        self.n_heads, self.dim, self.rot_dim, self.vdim, self.rank = n_heads, dim, rot_dim, vdim, kv_rank
+        self.scale, self.eps, self.window, self.chunk = float(scale), float(eps), window, chunk
+        self.rot_base, self.interleaved = float(rot_base), interleaved
+        self.q_head = dim + rot_dim
+        self.lat = kv_rank + rot_dim                      # what a score is taken over
+        self.row = (self.lat + 7) // 8 * 8                # a page row: whole 16 bytes
+        self.proj = FusedLinear(f"{name}.q_dkv", width, [(f"{name}.q", n_heads * self.q_head),
+                                                         (f"{name}.dkv", kv_rank + rot_dim)], init=init)
+        self.out = Linear(f"{name}.o", n_heads * vdim, width, bias=False, weight_suffix="", init=init)
+        self.init = init
+        self.norm_w = self.w_absorb = self.w_values = self.freq = None
+
+    def children(self):
+        return (self.proj, self.out)
+
+    def cache_spec(self):
+        return PagedKVSpec(1, self.row, self.window, chunk=self.chunk, value_dim=0)
+
+    def param_specs(self) -> List[ParamSpec]:
+        n, H, R = self.name, self.n_heads, self.rank
+        up = Init(0.0, R ** -0.5)
+        return [ParamSpec(f"{n}.dkv.norm", (R,), VECTOR, Init(1.0, 0.1)),
+                ParamSpec(f"{n}.uk", (H * self.dim, R), MATRIX, up),
+                ParamSpec(f"{n}.uv", (H * self.vdim, R), MATRIX, up)]
+
+    def bind(self, tensors, dtype, device) -> None:
+        n, H, R = self.name, self.n_heads, self.rank
+        self.norm_w = tensors[f"{n}.dkv.norm"]
+        # [H, rank, dim]: head h's matrix from its unrotated query to the latent columns
+        self.w_absorb = tensors[f"{n}.uk"].view(H, self.dim, R).transpose(1, 2).contiguous()
+        self.w_values = tensors[f"{n}.uv"].view(H, self.vdim, R).contiguous()
+        if self.rot_dim:
+            i = torch.arange(self.rot_dim // 2, dtype=torch.float64)
+            self.freq = (self.rot_base ** (-2.0 * i / self.rot_dim)).to(torch.float32).to(device)
+
+    def forward(self, ctx, x, residual, cache):
+        T, H, R = x.shape[0], self.n_heads, self.rank
+        n = self.proj.n_out
+        proj = ctx.ws.get("latent_proj", T, (n + 7) // 8 * 8, x.dtype)[:, :n]
+        self.proj.forward(ctx, x, proj)
+        q_lat = ctx.ws.get("latent_q", T, H * self.lat, torch.float32)
+        ops.label(self.name + ".prepare", 8.0 * T * n, x.element_size() * T * (n + self.row) + 4.0 * T * H * self.rot_dim)
+        ops.latent_prepare(proj, 0, H * self.q_head, H, self.dim, self.rot_dim, R, self.norm_w, self.eps, self.freq,
+                           self.interleaved, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.write, q_lat,
+                           self.lat, ctx.status, ctx.stream)
+        ops.label(self.name + ".uk", 2.0 * T * H * self.dim * R, x.element_size() * (T * H * self.dim + H * self.dim * R)
+                  + 4.0 * T * H * R)
+        ops.head_linear(proj, self.q_head, self.w_absorb, q_lat, self.lat, ctx.stream, token_req=ctx.token_req)
+        o_lat = ctx.ws.get("latent_o", T, H * R, torch.float32)
+        ops.label(self.name + ".attention")
+        ops.attention_wide(q_lat, self.lat, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.k, o_lat, R, H,
+                           self.lat, R, self.scale, ctx.status, ctx.stream, window=self.window or 0, chunk=self.chunk or 0)
+        o = ctx.ws.get("attn_out", T, H * self.vdim, x.dtype)
+        ops.label(self.name + ".uv", 2.0 * T * H * self.vdim * R, 4.0 * T * H * R + x.element_size() * (H * self.vdim * R
+                  + T * H * self.vdim))
+        ops.head_linear(o_lat, R, self.w_values, o, self.vdim, ctx.stream, token_req=ctx.token_req)
+        return self.out.forward(ctx, o, residual, residual=residual)
+
+
 register_part("mixer", "sink_attention", SinkAttention)
+register_part("mixer", "talking_heads_attention", TalkingHeadsAttention)
+register_part("mixer", "latent_attention", LatentAttention)
 register_part("mixer", "parallel", ParallelMixer)

@@ -171,5 +171,89 @@ class GatedDeltaMixer(Mixer):
         return self.out.forward(ctx, self._gated(ctx, x, cache), residual, residual=residual)
 
 
+class WKVMixer(Mixer):
+    """Time mixing in the manner of RWKV with a decay computed from the data.
+
+    With ``x'`` the row of the token before (zeros before the first token; the last row of a step is part of the
+    state), each of r, k, v, g, w reads its own mix ``x + (x' - x) mu_s`` (``<name>.mu.r`` ...).  ``r``, ``k``, ``v`` are
+    products of their mixes (``heads x dim`` each), the gate is ``silu(W_g mix_g)``, the decay per head and key channel
+    ``w = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0))``.  Per head, with a ``dim x dim`` state ``S``:
+    ``o_t = (S + diag(u) k_t v_t^T)^T r_t`` (the bonus ``u`` for the current token only), then
+    ``S <- diag(w_t) S + k_t v_t^T``.  Every head's ``o`` is divided by its root mean square, times ``<name>.norm``
+    (one weight per column), times the gate; then ``<name>.o``.  Decay, exponentials, state and the norm are float32."""
+    replayable = True
+    kernel_libs = ("wkv", "rms")
+    MIXES = ("r", "k", "v", "g", "w")
+
+    def __init__(self, name: str, width: int, n_heads: int, dim: int, decay_rank: int, eps: float, init: Init = Init()):
+        self.name, self.width, self.n_heads, self.dim, self.decay_rank, self.eps = name, width, n_heads, dim, decay_rank, float(eps)
+        self.inner = n_heads * dim
+        self.inner_p = (self.inner + 7) // 8 * 8      # sections of the shared buffers start on 16 bytes
+        self.width_p = (width + 7) // 8 * 8
+        lin = lambda s, n_in, n_out, i=init: Linear(f"{name}.{s}", n_in, n_out, bias=False, weight_suffix="", init=i)
+        self.r, self.k, self.v, self.g = (lin(s, width, self.inner) for s in "rkvg")
+        self.w1 = lin("w1", width, decay_rank)
+        self.w2 = lin("w2", decay_rank, self.inner, Init(0.0, decay_rank ** -0.5))
+        self.out = lin("o", self.inner, width, Init(0.0, self.inner ** -0.5))
+        self.mu = self.bonus = self.norm_w = None
+
+    def children(self):
+        return (self.r, self.k, self.v, self.g, self.w1, self.w2, self.out)
+
+    def cache_spec(self):
+        return {"shift": StateSpec((self.width,)),
+                "wkv": StateSpec((self.n_heads, self.dim, self.dim))}      # column by column: the scan's layout
+
+    def param_specs(self) -> List[ParamSpec]:
+        n = self.name
+        return ([ParamSpec(f"{n}.mu.{s}", (self.width,), VECTOR, Init(0.5, 0.2)) for s in self.MIXES]
+                + [ParamSpec(f"{n}.w0", (self.inner,), VECTOR, Init(-1.0, 1.0)),
+                   ParamSpec(f"{n}.u", (self.n_heads, self.dim), VECTOR, Init(0.0, 0.5)),
+                   ParamSpec(f"{n}.norm", (self.inner,), VECTOR, Init(1.0, 0.1))])
+
+    def bind(self, tensors, dtype, device) -> None:
+        n = self.name
+        self.mu = torch.stack([tensors[f"{n}.mu.{s}"] for s in self.MIXES]).contiguous()
+        self.bonus, self.norm_w = tensors[f"{n}.u"].contiguous(), tensors[f"{n}.norm"]
+
+    def bind_all(self, tensors, dtype, device) -> None:
+        super().bind_all(tensors, dtype, device)
+        self.w2.bias = tensors[f"{self.name}.w0"]   # the decay's offset is the bias of its second product
+
+    def _gated(self, ctx, x, cache):
+        T, D, HD, HDp, Dp = x.shape[0], self.width, self.inner, self.inner_p, self.width_p
+        shift, rule = cache.side("shift"), cache.side("wkv")
+        mixes = ctx.ws.get("wkv_mixes", T, len(self.MIXES) * Dp, x.dtype)
+        ops.label(self.name + ".shift", 2.0 * len(self.MIXES) * T * D, x.element_size() * (len(self.MIXES) + 1.0) * T * D)
+        ops.token_shift_mix(x, self.mu, shift.state, shift.slots, ctx.positions, ctx.token_req, ctx.req_first_token,
+                            mixes, ctx.stream)
+        rkvg = ctx.ws.get("wkv_rkvg", T, 4 * HDp, x.dtype)
+        for i, lin in enumerate((self.r, self.k, self.v, self.g)):
+            lin.forward(ctx, mixes[:, i * Dp:i * Dp + D], rkvg[:, i * HDp:i * HDp + HD])
+        L = self.decay_rank
+        lora = ctx.ws.get("wkv_lora", T, (L + 7) // 8 * 8, x.dtype)[:, :L]
+        self.w1.forward(ctx, mixes[:, 4 * Dp:4 * Dp + D], lora, activation="tanh")
+        decay = ctx.ws.get("wkv_decay", T, HD, torch.float32)
+        self.w2.forward(ctx, lora, decay)
+        o = ctx.ws.get("wkv_o", T, HD, torch.float32)
+        ops.label(self.name + ".scan", 6.0 * T * HD * self.dim, x.element_size() * 3.0 * T * HD + 8.0 * T * HD
+                  + 8.0 * min(T, ctx.n_requests) * HD * self.dim)
+        ops.wkv_scan(rkvg, 0, HDp, 2 * HDp, decay, self.bonus, rule.state, rule.slots, ctx.token_req, ctx.req_first_token,
+                     o, self.n_heads, ctx.stream)
+        gated = ctx.ws.get("wkv_gated", T, HD, x.dtype)
+        ops.label(self.name + ".norm", 8.0 * T * HD, (4.0 + 2 * x.element_size()) * T * HD)
+        ops.rmsnorm(o, self.norm_w, gated, self.eps, ctx.stream, groups=self.n_heads, gate=rkvg[:, 3 * HDp:3 * HDp + HD],
+                    gate_mode=ops.GATE_AFTER)
+        return gated
+
+    def mix(self, ctx, x, cache, tag: str = "mix_wkv"):
+        g = self._gated(ctx, x, cache)
+        return self.out.forward(ctx, g, ctx.ws.get(tag, x.shape[0], self.width, torch.float32))
+
+    def forward(self, ctx, x, residual, cache):
+        return self.out.forward(ctx, self._gated(ctx, x, cache), residual, residual=residual)
+
+
 register_part("mixer", "mamba2", Mamba2Mixer)
+register_part("mixer", "wkv", WKVMixer)
 register_part("mixer", "gated_delta", GatedDeltaMixer)

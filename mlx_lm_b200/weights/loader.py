@@ -104,6 +104,8 @@ def build_model(config: dict, tensors: Dict[str, torch.Tensor], dtype: torch.dty
         arch = get_architecture(config)
         build, args_class = arch.build, arch.args_class
     args = args_class.from_dict(config)
+    if hasattr(args, "sizes_from_tensors"):      # sizes that no key of the configuration gives, only a tensor's shape
+        args.sizes_from_tensors({_strip(n): tuple(t.shape) for n, t in tensors.items()})
     description = build(args)
     got = check_tensors(description, tensors)
     specs = {s.name: s for s in description.param_specs()}
