@@ -364,7 +364,7 @@ def kernel_table(calls, pk, mode, attention_bytes=0.0, attention_flops=0.0, reps
             us = max(time_graph(lead + group) - lead_us, 0.0) / len(group)
         flops = sum(c[4][1] for c in group if c[4]) / len(group)
         nbytes = sum(c[4][2] for c in group if c[4]) / len(group)
-        if kind.endswith("attention"):
+        if kind.endswith("attention") and not (flops or nbytes):      # a part that did not say: the caller's figures
             flops, nbytes = attention_flops, attention_bytes
         rec = {"n": len(group), "us": round(us, 2)}
         if us <= 0.0:          # lost in the noise of the launches it was timed behind (a model of very few layers)
@@ -665,10 +665,53 @@ def lelatar_config(width, vocab):
             "loop": {"start": 0, "stop": 4, "times": 2}, "layers": [mamba(None), par, mamba(ff), par, mamba(None), par]}
 
 
+def nufetar_config(width, vocab):
+    """Ten layers of the sizes a model of this width would have: heads of 64; attention with a quarter as many
+    key/value heads in runs of 1024 positions; latent rows of 256 + 32 columns in a window of 1024; a recurrence
+    with heads of 64 x 64; a feed-forward of about 2.7 times the width on every layer."""
+    H = width // 64
+    ff = {"ff": (width * 11 // 4 + 127) // 128 * 128, "kind": "dense"}
+    att = {"type": "attention", "mlp": ff,
+           "mixer": {"dim": 64, "heads": H, "kv_heads": max(1, H // 4), "vdim": 64, "scale": 0.125, "mask": {"size": 1024},
+                     "rot": {"base": 500000.0, "dims": 32}}}
+    lat = {"type": "latent_attention", "mlp": ff,
+           "mixer": {"dim": 64, "heads": H, "kv_rank": 256, "rot_dim": 32, "vdim": 64, "scale": 0.1, "mask": {"size": 1024},
+                     "rot": {"base": 500000.0, "dims": 32}}}
+    rec = {"type": "wkv", "mlp": ff, "mixer": {"dim": 64, "heads": H, "decay_rank": 64}}
+    return {"architecture": "Nufetar", "vocab": vocab, "width": width, "norm": {"eps": 1e-5},
+            "layers": [att, lat, lat, rec, att] * 2}
+
+
+def run_nufetar(args):
+    """The same measurements as ``--only lelatar`` for the Nufetar design, beside Lelatar (the nearest design in
+    the tree: a float32 stream, recurrent layers and attention layers side by side) at equal width and as many
+    layer runs."""
+    vocab = 32000
+
+    def models(width):
+        nuf = nufetar_config(width, vocab)
+        return len(nuf["layers"]), [("nufetar", nuf), ("lelatar", lelatar_config(width, vocab))]
+    run_beside(args, "nufetar_vs_lelatar", models)
+
+
 def run_lelatar(args):
     """Prefill (2 x 1024 tokens in one step) and decode (batch 8 and 64 at 512 tokens of context, through
     Engine.step) of Lelatar models with random weights at two widths, beside GPT-2 models of the same width and
     as many layer runs, and the kernels of both timed alone against their rooflines."""
+    vocab = 32000
+
+    def models(width):
+        lel = lelatar_config(width, vocab)
+        runs = len(lel["layers"]) + (lel["loop"]["times"] - 1) * (lel["loop"]["stop"] - lel["loop"]["start"])
+        gpt = dict(model_type="gpt2", n_layer=runs, n_embd=width, n_head=width // 64, n_inner=4 * width, vocab_size=vocab,
+                   n_positions=2048, layer_norm_epsilon=1e-5, activation_function="gelu_new")
+        return runs, [("lelatar", lel), ("gpt2", gpt)]
+    run_beside(args, "lelatar_vs_gpt2", models)
+
+
+def run_beside(args, metric, models):
+    """``models(width) -> (layer runs, [(name, config), ...])``: every model's prefill and decode steps and its
+    kernels, one JSON line."""
     import torch
 
     from mlx_lm_b200.engine import Engine, StepEntry
@@ -677,14 +720,11 @@ def run_lelatar(args):
 
     pk = peaks()
     vocab = 32000
-    out = {"metric": "lelatar_vs_gpt2", "dtype": "bf16", "data": "synthetic", "peaks": pk, "models": []}
+    out = {"metric": metric, "dtype": "bf16", "data": "synthetic", "peaks": pk, "models": []}
     widths = [int(w) for w in (args.widths.split(",") if args.widths else ["1024", "2048"])]
     for width in widths:
-        lel = lelatar_config(width, vocab)
-        runs = len(lel["layers"]) + (lel["loop"]["times"] - 1) * (lel["loop"]["stop"] - lel["loop"]["start"])
-        gpt = dict(model_type="gpt2", n_layer=runs, n_embd=width, n_head=width // 64, n_inner=4 * width, vocab_size=vocab,
-                   n_positions=2048, layer_norm_epsilon=1e-5, activation_function="gelu_new")
-        for name, cfg in (("lelatar", lel), ("gpt2", gpt)):
+        runs, pairs = models(width)
+        for name, cfg in pairs:
             arch = get_architecture(cfg)
             description = arch.build(arch.args_class.from_dict(dict(cfg)))
             model = build_model(dict(cfg), random_tensors(description, 0), torch.bfloat16, "cuda")
@@ -752,9 +792,9 @@ def main():
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration's 24 (0 = all)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--widths", default="", help="with --only lelatar: the model widths to run, with commas (default 1024,2048)")
+    ap.add_argument("--widths", default="", help="with --only lelatar / nufetar: the model widths to run, with commas (default 1024,2048)")
     ap.add_argument("--only", default="", choices=["", "decode", "prefill", "mixed", "timeline", "kernels", "yardstick",
-                                                   "lelatar"],
+                                                   "lelatar", "nufetar"],
                     help="run just this part and print its figures (decode / prefill: short runs for profiling; "
                          "mixed: 64 requests with prompts of 16..1024 tokens through the scheduler, 256-token portions "
                          "beside decoding requests; timeline: every kernel of one step with its start and end, "
@@ -762,7 +802,7 @@ def main():
                          "alone, with bytes, flops and the fraction of the measured peak; yardstick: torch.matmul on the "
                          "model's linear shapes, to hold the hand-written kernels against; lelatar: prefill and decode of "
                          "the Lelatar design at two widths beside GPT-2 of equal width and layer runs, with every kernel "
-                         "of both against its roofline)")
+                         "of both against its roofline; nufetar: the same for the Nufetar design beside Lelatar)")
     ap.add_argument("--prefill-prompts", type=int, default=0,
                     help="with --only prefill: 1024-token prompts in the one step (default and the contract's figure: "
                          "2); with --only timeline: the timeline of such a step instead of a decode step")
@@ -780,6 +820,9 @@ def main():
     a.warmup = max(a.warmup, 3)
     if a.only == "lelatar":
         run_lelatar(a)
+        return 0
+    if a.only == "nufetar":
+        run_nufetar(a)
         return 0
     run_ours(a)
     return 0

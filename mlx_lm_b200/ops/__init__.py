@@ -134,6 +134,11 @@ def label(name: str, flops: float = 0.0, nbytes: float = 0.0) -> None:
         _label = (name, float(flops), float(nbytes))
 
 
+def recording() -> bool:
+    """Whether launches are being noted (and labels kept) right now."""
+    return _recording is not None
+
+
 def start_recording() -> None:
     """Begin to note every launch with its raw arguments, so that a step of the same shape can be
     re-issued later without going through the checks and the parts again (``replay``)."""

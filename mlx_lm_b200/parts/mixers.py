@@ -253,6 +253,21 @@ class ParallelMixer(Mixer):
         return residual
 
 
+def visible_pairs(ctx, window: Optional[int], chunk: Optional[int]):
+    """For a label: how many (query, key) pairs this step's queries see, and how many distinct keys they read."""
+    pairs = keys = 0
+    for sp in ctx.spans:
+        first = None
+        for p in range(sp.first_position, sp.first_position + sp.n_tokens):
+            lo = max(0, p - window + 1) if window else 0
+            if chunk:
+                lo = max(lo, p // chunk * chunk)
+            pairs += p - lo + 1
+            first = lo if first is None else min(first, lo)
+        keys += sp.first_position + sp.n_tokens - (first or 0)
+    return pairs, keys
+
+
 class TalkingHeadsAttention(Mixer):
     """Grouped-query causal attention in which a CTA of the attention kernel takes all heads of a query
     (``ops.attention_wide``), with these options, each a parameter:
@@ -332,7 +347,10 @@ class TalkingHeadsAttention(Mixer):
         ops.label(self.name + ".prepare", 8.0 * T * n, (x.element_size() + 4.0) * T * n)
         self._prepare(ctx, proj, cache, q)
         o = ctx.ws.get("attn_out", T, H * self.vdim, x.dtype)
-        ops.label(self.name + ".attention")
+        if ops.recording():
+            pairs, keys = visible_pairs(ctx, self.window, self.chunk)
+            ops.label(self.name + ".attention", pairs * H * (2.0 * self.dim + 2.0 * self.vdim + 2.0 * H),
+                      x.element_size() * (keys * G * (self.key_row + self.value_row) + T * H * self.vdim) + 4.0 * T * H * self.dim)
         g_off = (H + G) * self.dim + G * self.vdim
         ops.attention_wide(q, self.key_row, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o, self.vdim,
                            H, self.dim, self.vdim, self.scale, ctx.status, ctx.stream, window=self.window or 0,
@@ -420,7 +438,10 @@ class LatentAttention(Mixer):
                   + 4.0 * T * H * R)
         ops.head_linear(proj, self.q_head, self.w_absorb, q_lat, self.lat, ctx.stream, token_req=ctx.token_req)
         o_lat = ctx.ws.get("latent_o", T, H * R, torch.float32)
-        ops.label(self.name + ".attention")
+        if ops.recording():
+            pairs, keys = visible_pairs(ctx, self.window, self.chunk)
+            ops.label(self.name + ".attention", pairs * H * 2.0 * (self.lat + R),
+                      x.element_size() * keys * self.row + 4.0 * T * H * (self.lat + R))
         ops.attention_wide(q_lat, self.lat, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.k, o_lat, R, H,
                            self.lat, R, self.scale, ctx.status, ctx.stream, window=self.window or 0, chunk=self.chunk or 0)
         o = ctx.ws.get("attn_out", T, H * self.vdim, x.dtype)
