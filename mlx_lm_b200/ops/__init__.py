@@ -49,7 +49,7 @@ _DT = {torch.float32: F32, torch.bfloat16: BF16}
 
 # kernel sources that only a bfloat16 run launches from: a float32 run neither compiles nor loads them
 BF16_ONLY_LIBS = frozenset({"gemm_smallm", "gemm_smallm_fold", "gemm_tcgen05", "attention_prefill",
-                            "attention_prefill_tc"})
+                            "attention_prefill_tc", "attention_wide_tc"})
 
 # status word bits set by kernels (csrc/common.cuh)
 ST_TOKEN_RANGE, ST_POSITION_RANGE, ST_PAGE_RANGE, ST_WAIT_TIMEOUT = 1, 2, 4, 8
@@ -943,6 +943,75 @@ def attention_wide(q, q_head_stride: int, positions, token_req, block_table, k_p
           _p(token_req), _p(block_table), block_table.shape[1], n_pages, page, n_heads, Hkv, key_dim, value_dim, krs, vrs,
           int(window or 0), int(chunk or 0), float(scale), _p(talk), _p(k_pool), _p(v_pool), _p(gate), ldg, _p(out),
           _rows(out, "attention_wide out"), out_head_stride, _p(rows), n, _p(status), stream)
+
+
+_WIDE_TC_ARGS = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                 c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
+                 c_int, c_void_p, c_void_p]
+
+WIDE_TC = _os.environ.get("MLXB_WIDE_TC", "1") != "0"     # 0: the kernel on the CUDA cores for bfloat16 too
+
+
+def attention_wide_tc_supported(k_pool, v_pool, n_heads: int, key_dim: int, value_dim: int, talk: bool) -> bool:
+    """Whether ``attention_wide_tiles`` serves these sizes (bfloat16 pools, widths in whole 16-byte pieces, at most
+    512 value columns, a tile that fits the shared memory)."""
+    if not WIDE_TC or k_pool.dtype != torch.bfloat16:
+        return False
+    f, _ = _fn("attention_wide_tc", "mlxb_attention_wide_tc_supported", [c_int] * 8)
+    return bool(f(n_heads, k_pool.shape[1], key_dim, value_dim, k_pool.shape[3], v_pool.shape[3], int(talk),
+                  int(v_pool.data_ptr() == k_pool.data_ptr())))
+
+
+def attention_wide_tiles(q, q_head_stride: int, tiles, n_tiles: int, tile_queries: int, block_table, k_pool, v_pool, out,
+                         out_head_stride: int, n_heads: int, key_dim: int, value_dim: int, scale: float, status, stream,
+                         window: int = 0, chunk: int = 0, talk=None, gate=None) -> None:
+    """``attention_wide`` on tensor cores for bfloat16 pools.  Instead of token rows it takes tiles, int32
+    ``[n_tiles, 4]`` = (first token row, queries, block-table row, first position) of at most ``tile_queries``
+    consecutive tokens of one request each (tiles of 0 queries are skipped)."""
+    _need(q, torch.float32, "attention_wide_tiles q")
+    _need(k_pool, torch.bfloat16, "attention_wide_tiles k_pool")
+    _need(v_pool, torch.bfloat16, "attention_wide_tiles v_pool")
+    _need(tiles, torch.int32, "attention_wide_tiles tiles")
+    n_pages, Hkv, page, krs = k_pool.shape
+    if v_pool.shape[:3] != k_pool.shape[:3] or not (k_pool.is_contiguous() and v_pool.is_contiguous()):
+        raise KernelError(f"attention_wide_tiles: pools {tuple(k_pool.shape)} and {tuple(v_pool.shape)}")
+    if out.dtype not in (torch.bfloat16, torch.float32) or out.shape[0] != q.shape[0] or tiles.numel() < 4 * n_tiles:
+        raise KernelError(f"attention_wide_tiles: out {out.dtype} {tuple(out.shape)} for q {tuple(q.shape)}")
+    if talk is not None:
+        _need(talk, torch.float32, "attention_wide_tiles talk")
+        if talk.shape != (n_heads, n_heads) or not talk.is_contiguous():
+            raise KernelError(f"attention_wide_tiles: talk {tuple(talk.shape)} for {n_heads} heads")
+    ldg = 0
+    if gate is not None:
+        _need(gate, torch.bfloat16, "attention_wide_tiles gate")
+        if gate.shape[1] != n_heads:
+            raise KernelError(f"attention_wide_tiles: gate {tuple(gate.shape)} for {n_heads} heads")
+        ldg = _rows(gate, "attention_wide_tiles gate")
+    _call("attention_wide_tc", "mlxb_attention_wide_tc", _WIDE_TC_ARGS, int(out.dtype == torch.float32), _p(q),
+          _rows(q, "attention_wide_tiles q"), q_head_stride, _p(tiles), n_tiles, tile_queries, _p(block_table),
+          block_table.shape[1], n_pages, page, n_heads, Hkv, key_dim, value_dim, krs, v_pool.shape[3], int(window or 0),
+          int(chunk or 0), float(scale), _p(talk), _p(k_pool), _p(v_pool), _p(gate), ldg, _p(out),
+          _rows(out, "attention_wide_tiles out"), out_head_stride, _p(status), stream)
+
+
+def attention_wide_step(ctx, q, q_head_stride: int, cache_k, cache_v, block_table, out, out_head_stride: int, n_heads: int,
+                        key_dim: int, value_dim: int, scale: float, window: int = 0, chunk: int = 0, talk=None,
+                        gate=None) -> None:
+    """All of a step's rows through ``attention_wide``: on tensor cores where the sizes allow it (the portions' tiles
+    and the single-token rows are two launches), else on the CUDA cores (float32 runs, odd sizes)."""
+    if attention_wide_tc_supported(cache_k, cache_v, n_heads, key_dim, value_dim, talk is not None):
+        if ctx.n_portion and ctx.portion_tiles is not None:
+            attention_wide_tiles(q, q_head_stride, ctx.portion_tiles, ctx.n_portion_tiles, PREFILL_TILE, block_table,
+                                 cache_k, cache_v, out, out_head_stride, n_heads, key_dim, value_dim, scale, ctx.status,
+                                 ctx.stream, window=window, chunk=chunk, talk=talk, gate=gate)
+        if ctx.n_single and ctx.single_tiles is not None:
+            attention_wide_tiles(q, q_head_stride, ctx.single_tiles, ctx.n_single, 1, block_table, cache_k, cache_v, out,
+                                 out_head_stride, n_heads, key_dim, value_dim, scale, ctx.status, ctx.stream,
+                                 window=window, chunk=chunk, talk=talk, gate=gate)
+        return
+    attention_wide(q, q_head_stride, ctx.positions, ctx.token_req, block_table, cache_k, cache_v, out, out_head_stride,
+                   n_heads, key_dim, value_dim, scale, ctx.status, ctx.stream, window=window, chunk=chunk, talk=talk,
+                   gate=gate)
 
 
 # --------------------------------------------------------------------------

@@ -287,7 +287,7 @@ class TalkingHeadsAttention(Mixer):
 
     Queries go to the kernel in float32; scores, their mix and the softmax are float32."""
     replayable = True
-    kernel_libs = ("attention_wide", "rotary")
+    kernel_libs = ("attention_wide", "attention_wide_tc", "rotary")
 
     def __init__(self, name: str, width: int, n_heads: int, n_kv_heads: int, dim: int, vdim: int, scale: float,
                  eps: float, rot_dims: int = 0, rot_base: float = 10000.0, interleaved: bool = False, bias: bool = True,
@@ -352,10 +352,9 @@ class TalkingHeadsAttention(Mixer):
             ops.label(self.name + ".attention", pairs * H * (2.0 * self.dim + 2.0 * self.vdim + 2.0 * H),
                       x.element_size() * (keys * G * (self.key_row + self.value_row) + T * H * self.vdim) + 4.0 * T * H * self.dim)
         g_off = (H + G) * self.dim + G * self.vdim
-        ops.attention_wide(q, self.key_row, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.v, o, self.vdim,
-                           H, self.dim, self.vdim, self.scale, ctx.status, ctx.stream, window=self.window or 0,
-                           chunk=self.chunk or 0, talk=self.talk,
-                           gate=proj[:, g_off:g_off + H] if self.head_gate else None)
+        ops.attention_wide_step(ctx, q, self.key_row, cache.k, cache.v, cache.block_table, o, self.vdim, H, self.dim,
+                                self.vdim, self.scale, window=self.window or 0, chunk=self.chunk or 0, talk=self.talk,
+                                gate=proj[:, g_off:g_off + H] if self.head_gate else None)
         return self.out.forward(ctx, o, residual, residual=residual)
 
     def _prepare(self, ctx, proj, cache, q) -> None:
@@ -381,7 +380,7 @@ class LatentAttention(Mixer):
     attention's output stay float32 between those products.  Rotation pairs ``(2i, 2i+1)`` (``interleaved``) or
     ``(i, i + rot_dim/2)``; ``window`` as in the other attention parts."""
     replayable = True
-    kernel_libs = ("attention_wide", "latent")
+    kernel_libs = ("attention_wide", "attention_wide_tc", "latent")
 
     def __init__(self, name: str, width: int, n_heads: int, dim: int, rot_dim: int, vdim: int, kv_rank: int,
                  scale: float, eps: float, rot_base: float = 10000.0, interleaved: bool = True,
@@ -442,8 +441,8 @@ class LatentAttention(Mixer):
             pairs, keys = visible_pairs(ctx, self.window, self.chunk)
             ops.label(self.name + ".attention", pairs * H * 2.0 * (self.lat + R),
                       x.element_size() * keys * self.row + 4.0 * T * H * (self.lat + R))
-        ops.attention_wide(q_lat, self.lat, ctx.positions, ctx.token_req, cache.block_table, cache.k, cache.k, o_lat, R, H,
-                           self.lat, R, self.scale, ctx.status, ctx.stream, window=self.window or 0, chunk=self.chunk or 0)
+        ops.attention_wide_step(ctx, q_lat, self.lat, cache.k, cache.k, cache.block_table, o_lat, R, H, self.lat, R,
+                                self.scale, window=self.window or 0, chunk=self.chunk or 0)
         o = ctx.ws.get("attn_out", T, H * self.vdim, x.dtype)
         ops.label(self.name + ".uv", 2.0 * T * H * self.vdim * R, 4.0 * T * H * R + x.element_size() * (H * self.vdim * R
                   + T * H * self.vdim))

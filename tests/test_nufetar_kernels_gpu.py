@@ -30,6 +30,29 @@ def paged(rows, n_heads, width, page, dtype, n_pages, order):
     return pool
 
 
+def check_tiles(ops, qd, qhs, table, kp, vp, H, dk, dv, scale, window, chunk, talk, gate, want, T):
+    """The tensor-core kernel over the same request: as portions in tiles of up to 128 queries (one of them cut short,
+    one empty), and as single-token rows; float32 and bfloat16 outputs."""
+    status = torch.zeros(1, dtype=torch.int32, device=DEV)
+    tiles = i32([[128, T - 128, 0, 128], [0, 0, 0, 0], [0, 128, 0, 0]])
+    for out_dtype in (torch.float32, torch.bfloat16):
+        out = torch.full((T, H * dv), 7.0, dtype=out_dtype, device=DEV)
+        ops.attention_wide_tiles(qd, qhs, tiles, 3, 128, table, kp, vp, out, dv, H, dk, dv, scale, status,
+                                 ops.current_stream(), window=window, chunk=chunk, talk=talk, gate=gate)
+        assert int(status.item()) == 0
+        err = float((out.double().cpu().view(T, H, dv) - want).abs().max())
+        assert err < (6e-3 if out_dtype == torch.float32 else 2e-2), ("tiles", out_dtype, err)
+    rows = [0, 1, 63, 64, 65, 127, 128, T - 1]
+    singles = i32([[r, 1, 0, r] for r in rows] + [[5, 0, 0, 0]])
+    out = torch.full((T, H * dv), 7.0, device=DEV)
+    ops.attention_wide_tiles(qd, qhs, singles, len(rows) + 1, 1, table, kp, vp, out, dv, H, dk, dv, scale, status,
+                             ops.current_stream(), window=window, chunk=chunk, talk=talk, gate=gate)
+    assert int(status.item()) == 0
+    got = out.double().cpu().view(T, H, dv)
+    assert float((got[rows] - want[rows]).abs().max()) < 6e-3
+    assert bool((out[5] == 7.0).all()) and bool((out[2] == 7.0).all())
+
+
 @pytest.mark.parametrize("act", ACT)
 @pytest.mark.parametrize("H,G,dk,dv,window,chunk,talk,gate", [
     (4, 2, 32, 16, 0, 24, True, True),
@@ -73,6 +96,11 @@ def test_attention_with_a_group_of_heads(act, H, G, dk, dv, window, chunk, talk,
         assert int(status.item()) == 0
         err = float((out.double().cpu().view(T, H, dv) - want).abs().max())
         assert err < (2e-5 if out_dtype == torch.float32 else 2e-2), (out_dtype, err)
+    if act == torch.bfloat16:
+        assert ops.attention_wide_tc_supported(kp, vp, H, dk, dv, talk) == (dk % 8 == 0 and dv % 8 == 0)
+        if ops.attention_wide_tc_supported(kp, vp, H, dk, dv, talk):
+            check_tiles(ops, qd, krow, table, kp, vp, H, dk, dv, scale, window, chunk,
+                        Tm.to(DEV).contiguous() if talk else None, gt.to(act).to(DEV) if gate else None, want, T)
     # a row that pads the step is skipped; a subset of rows leaves the others alone
     out = torch.full((T, H * dv), 7.0, device=DEV)
     req = [0] * T
@@ -109,6 +137,17 @@ def test_attention_reads_values_out_of_the_key_rows(act, H, R, dr, window):
                        R, H, lat, R, scale, status, ops.current_stream(), window=window)
     assert int(status.item()) == 0
     assert float((out.double().cpu().view(T, H, R) - want).abs().max()) < 3e-5
+    if act == torch.bfloat16 and R % 8 == 0:
+        assert ops.attention_wide_tc_supported(pool, pool, H, lat, R, False)
+        qd = q.reshape(T, H * lat).to(DEV)
+        for tiles, n, tq, rows in ((i32([[0, T, 0, 0]]), 1, 128, list(range(T))),
+                                   (i32([[r, 1, 0, r] for r in (0, 1, 17, 63, 64, T - 1)]), 6, 1, [0, 1, 17, 63, 64, T - 1])):
+            out = torch.zeros(T, H * R, device=DEV)
+            ops.attention_wide_tiles(qd, lat, tiles, n, tq, i32([order]), pool, pool, out, R, H, lat, R, scale, status,
+                                     ops.current_stream(), window=window)
+            assert int(status.item()) == 0
+            got = out.double().cpu().view(T, H, R)
+            assert float((got[rows] - want[rows]).abs().max()) < 6e-3      # the weights are rounded to bfloat16
 
 
 @pytest.mark.parametrize("act", ACT)
