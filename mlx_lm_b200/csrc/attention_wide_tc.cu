@@ -55,7 +55,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
                          int Dk, int Dv, int DkE, int seg, int n_seg, int krs, int vrs, int shared_v, int window,
                          int chunk, float scale, const float* __restrict__ talk, const __nv_bfloat16* k_pool,
                          const __nv_bfloat16* v_pool, const __nv_bfloat16* gate, int ldg, TO* __restrict__ out, int ldo,
-                         int ohs, int* __restrict__ status) {
+                         int ohs, int* __restrict__ status, int bps, int n_rel, float* __restrict__ scratch) {
   extern __shared__ __align__(16) unsigned char tc_smem[];
   const int ldk = DkE + 8, ldv = shared_v ? ldk : Dv + 8;
   long long* sRow = reinterpret_cast<long long*>(tc_smem);                  // [TC_N]
@@ -75,6 +75,10 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
   const int t0 = t_first + sub * TQ, pos0 = tiles[4 * tile + 3] + sub * TQ;
   const int h0 = blockIdx.y * HG, rep = Hq / Hkv, cv = h0 / rep;
   const int* bt = block_table + (size_t)bt_row * max_pages;
+  int lo_min = 0;                                            // first visible key of the first token: the smallest of the CTA
+  if (window > 0 && pos0 - window + 1 > lo_min) lo_min = pos0 - window + 1;
+  if (chunk > 0 && (pos0 / chunk) * chunk > lo_min) lo_min = (pos0 / chunk) * chunk;
+  if (bps > 0 && ((lo_min / TC_N) / bps + (int)blockIdx.z) * bps * TC_N > pos0 + nq - 1) return;   // a split without keys
   pdl_wait();
   pdl_trigger();
   q = after_wait(q);
@@ -107,10 +111,15 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
   int my_lo = 0;
   if (window > 0 && my_p - window + 1 > my_lo) my_lo = my_p - window + 1;
   if (chunk > 0 && (my_p / chunk) * chunk > my_lo) my_lo = (my_p / chunk) * chunk;
-  int lo_min = 0;                                            // of the first token: the smallest of the CTA
-  if (window > 0 && pos0 - window + 1 > lo_min) lo_min = pos0 - window + 1;
-  if (chunk > 0 && (pos0 / chunk) * chunk > lo_min) lo_min = (pos0 / chunk) * chunk;
-  const int p_max = pos0 + nq - 1;
+  int p_max = pos0 + nq - 1;
+  int j_first = (lo_min / TC_N) * TC_N;
+  if (bps > 0) {
+    // single rows with their keys split over the CTAs of grid.z: this one takes the blocks bps*za .. bps*za + bps - 1,
+    // counted from position 0, and leaves an unnormalised partial result for the merge kernel
+    const int za = (lo_min / TC_N) / bps + blockIdx.z;
+    j_first = max(j_first, za * bps * TC_N);
+    p_max = min(p_max, (za + 1) * bps * TC_N - 1);
+  }
   float m_run = -INFINITY, l_run = 0.f;
   float o[TC_NT][2][4];
 #pragma unroll
@@ -122,7 +131,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
   const int n_vt = Dv / 8;                                   // 8-column tiles of the values
   const int g = lane >> 2, tq4 = lane & 3;
 
-  for (int j0 = (lo_min / TC_N) * TC_N; j0 <= p_max; j0 += TC_N) {
+  for (int j0 = j_first; j0 <= p_max; j0 += TC_N) {
     __syncthreads();                                         // the block before is done with the tiles
     if (tid < TC_N) {
       const int j = j0 + tid;
@@ -255,6 +264,31 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
   }
   if (my_sub == 0) sL[my_row] = l_run;
   __syncthreads();
+  if (bps > 0) {
+    // partial results (TQ = 1: row r is head h0 + r): [tile, head, split][Dv values | maximum | sum]
+    const size_t stride = (size_t)Dv + 2;
+    if (my_sub == 0 && my_row < HG) {
+      float* sp = scratch + (((size_t)tile * Hq + h0 + my_row) * n_rel + blockIdx.z) * stride;
+      sp[Dv] = m_run;
+      sp[Dv + 1] = l_run;
+    }
+#pragma unroll
+    for (int i = 0; i < TC_NT; ++i) {
+      const int nt = warp + i * TC_WARPS;
+      if (nt >= n_vt) continue;
+#pragma unroll
+      for (int m = 0; m < 2; ++m)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+          const int r = m * 16 + g + half * 8;
+          if (r >= HG) continue;
+          float* sp = scratch + (((size_t)tile * Hq + h0 + r) * n_rel + blockIdx.z) * stride + nt * 8 + tq4 * 2;
+          sp[0] = o[i][m][half * 2];
+          sp[1] = o[i][m][half * 2 + 1];
+        }
+    }
+    return;
+  }
 #pragma unroll
   for (int i = 0; i < TC_NT; ++i) {
     const int nt = warp + i * TC_WARPS;
@@ -275,6 +309,60 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
         op[1] = from_f<TO>(o[i][m][half * 2 + 1] * f);
       }
   }
+}
+
+// The partial results of a single row's splits, merged in the order of the splits: one block per (tile, head).
+template <typename TO>
+__global__ void attention_wide_merge_kernel(const int* __restrict__ tiles, int Hq, int Dv, int window, int chunk, int bps,
+                                            int n_rel, const float* scratch, const __nv_bfloat16* gate, int ldg,
+                                            TO* __restrict__ out, int ldo, int ohs) {
+  const int tile = blockIdx.x, h = blockIdx.y;
+  if (tiles[4 * tile + 1] <= 0) return;
+  const int t = tiles[4 * tile], p = tiles[4 * tile + 3];
+  int lo = 0;
+  if (window > 0 && p - window + 1 > lo) lo = p - window + 1;
+  if (chunk > 0 && (p / chunk) * chunk > lo) lo = (p / chunk) * chunk;
+  const int nz = (p / TC_N) / bps - (lo / TC_N) / bps + 1;
+  pdl_wait();
+  pdl_trigger();
+  scratch = after_wait(scratch);
+  gate = after_wait(gate);
+  const size_t stride = (size_t)Dv + 2;
+  const float* sp = scratch + ((size_t)tile * Hq + h) * n_rel * stride;
+  float M = -INFINITY;
+  for (int z = 0; z < nz; ++z) M = fmaxf(M, sp[z * stride + Dv]);
+  float L = 0.f;
+  for (int z = 0; z < nz; ++z) {
+    const float mz = sp[z * stride + Dv];
+    if (mz != -INFINITY) L = fmaf(expf(mz - M), sp[z * stride + Dv + 1], L);
+  }
+  float f = L > 0.f ? 1.f / L : 0.f;
+  if (gate) f *= 1.f / (1.f + expf(-__bfloat162float(gate[(size_t)t * ldg + h])));
+  for (int c = threadIdx.x; c < Dv; c += blockDim.x) {
+    float a = 0.f;
+    for (int z = 0; z < nz; ++z) {
+      const float mz = sp[z * stride + Dv];
+      if (mz != -INFINITY) a = fmaf(expf(mz - M), sp[z * stride + c], a);
+    }
+    out[(size_t)t * ldo + (size_t)h * ohs + c] = from_f<TO>(a * f);
+  }
+}
+
+constexpr int TC_BPS = 2;     // key blocks a CTA of a split single row takes: a constant, never a function of the batch
+
+// Splits a single row can have: the positions it can see, in blocks, over TC_BPS, and one more at either end.
+static int tc_splits(int window, int chunk, int max_len) {
+  int span = max_len > 0 ? max_len : 1;
+  if (window > 0 && window < span) span = window;
+  if (chunk > 0 && chunk < span) span = chunk;
+  return ((span + TC_N - 1) / TC_N + 1) / TC_BPS + 2;
+}
+
+// Floats of scratch memory that single rows need (0: rows that see at most two blocks are not split).
+MLXB_EXPORT long long mlxb_attention_wide_tc_scratch(int n_rows, int Hq, int Dv, int window, int chunk, int max_len) {
+  const int n_rel = tc_splits(window, chunk, max_len);
+  if (n_rel <= 3) return 0;
+  return (long long)n_rows * Hq * n_rel * (Dv + 2);
 }
 
 // What the launch needs of shared memory, or -1 if the sizes are not served (the caller then takes the kernel on the
@@ -314,7 +402,8 @@ MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int
                                        int tile_q, const int* block_table, int max_pages, int n_pages, int page, int Hq,
                                        int Hkv, int Dk, int Dv, int krs, int vrs, int window, int chunk, float scale,
                                        const float* talk, const void* k_pool, const void* v_pool, const void* gate,
-                                       int ldg, void* out, int ldo, int ohs, int* status, cudaStream_t stream) {
+                                       int ldg, void* out, int ldo, int ohs, int* status, float* scratch, int max_len,
+                                       cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   int DkE, seg, n_seg, HG;
   const int shared_v = v_pool == k_pool;
@@ -322,9 +411,13 @@ MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int
   if (smem < 0 || page <= 0 || (page & (page - 1)) || tile_q <= 0 || qhs < Dk || ohs < Dv)
     return mlxb_fail(MLXB_BAD_ARG, "attention (wide, tensor cores): %d/%d heads, sizes %d/%d in rows of %d/%d", Hq, Hkv,
                      Dk, Dv, krs, vrs);
-  const int TQ = TC_M / HG;
+  // single rows with scratch memory: their keys split over grid.z, then merged
+  const int n_rel = tc_splits(window, chunk, max_len);
+  const bool split = tile_q == 1 && scratch != nullptr && n_rel > 3;
+  const int TQ = split ? 1 : TC_M / HG;
   const int subs = (tile_q + TQ - 1) / TQ;
-  const dim3 grid((unsigned)n_tiles * subs, Hq / HG), block(TC_THREADS);
+  const int bps = split ? TC_BPS : 0;
+  const dim3 grid((unsigned)n_tiles * subs, Hq / HG, split ? n_rel : 1), block(TC_THREADS);
 #define TCW_GO(TO)                                                                                                     \
   do {                                                                                                                 \
     auto kern = attention_wide_tc_kernel<TO>;                                                                          \
@@ -337,7 +430,13 @@ MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int
     launch_pdl(kern, grid, block, (size_t)smem, stream, q, ldq, qhs, tiles, subs, TQ, HG, block_table, max_pages,      \
                n_pages, page, Hq, Hkv, Dk, Dv, DkE, seg, n_seg, krs, vrs, shared_v, window, chunk, scale, talk,        \
                (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate, ldg, (TO*)out,  \
-               ldo, ohs, status);                                                                                      \
+               ldo, ohs, status, bps, n_rel, scratch);                                                                 \
+    if (split) {                                                                                                       \
+      if (int e = mlxb_check_launch("attention (wide, tensor cores)")) return e;                                       \
+      launch_pdl(attention_wide_merge_kernel<TO>, dim3(n_tiles, Hq), dim3(Dv >= 128 ? 128 : 64), 0, stream, tiles, Hq, \
+                 Dv, window, chunk, bps, n_rel, (const float*)scratch, (const __nv_bfloat16*)gate, ldg, (TO*)out, ldo, \
+                 ohs);                                                                                                 \
+    }                                                                                                                  \
   } while (0)
   if (out_f32) TCW_GO(float);
   else TCW_GO(__nv_bfloat16);

@@ -157,6 +157,37 @@ head_linear_kernel(const TX* x, int ldx, int xhs, const TW* __restrict__ w, TO* 
   }
 }
 
+// The same for steps of few rows (single-token entries): a warp per output column and eight rows, the lanes side by
+// side along k (the weights are read once, in whole lines), partial sums added across the warp.
+template <typename TX, typename TW, typename TO>
+__global__ void __launch_bounds__(256)
+head_linear_rows_kernel(const TX* x, int ldx, int xhs, const TW* __restrict__ w, TO* __restrict__ out, int ldo, int ohs,
+                        int M, int N, int K, const int* __restrict__ token_req) {
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int n = blockIdx.x * 8 + warp, h = blockIdx.y, m0 = blockIdx.z * 8;
+  pdl_wait();
+  pdl_trigger();
+  x = after_wait(x);
+  if (n >= N) return;
+  const TW* wr = w + ((size_t)h * N + n) * K;
+  const TX* xh = x + (size_t)h * xhs;
+  float acc[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) acc[i] = 0.f;
+  for (int k = lane; k < K; k += 32) {
+    const float wv = to_f(wr[k]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (m0 + i < M) acc[i] = fmaf(to_f(xh[(size_t)(m0 + i) * ldx + k]), wv, acc[i]);
+  }
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float v = warp_sum(acc[i]);
+    const int m = m0 + i;
+    if (lane == 0 && m < M && !(token_req && token_req[m] < 0)) out[(size_t)m * ldo + (size_t)h * ohs + n] = from_f<TO>(v);
+  }
+}
+
 // x: [M, .] at row stride ldx, head h from column h*xhs (K values), float32 if x_f32 else `dtype`; w: `dtype`
 // [H, N, K]; out: [M, .] at row stride ldo, head h from column h*ohs (N values), float32 if out_f32 else `dtype`;
 // token_req: int32 [M] or null: rows whose entry is negative are not written.
@@ -166,16 +197,21 @@ MLXB_EXPORT int mlxb_head_linear(int dtype, int x_f32, int out_f32, const void* 
   if (M <= 0) return 0;
   if (N <= 0 || K <= 0 || H <= 0 || xhs < K || ohs < N || H > 65535)
     return mlxb_fail(MLXB_BAD_ARG, "head_linear: %d heads of %d x %d, head strides %d / %d", H, N, K, xhs, ohs);
-  const dim3 grid((N + HL_TN - 1) / HL_TN, (M + HL_TM - 1) / HL_TM, H), block(256);
+  const bool few = M <= 16;
+  const dim3 grid((N + HL_TN - 1) / HL_TN, (M + HL_TM - 1) / HL_TM, H), rgrid((N + 7) / 8, H, (M + 7) / 8), block(256);
 #define HL_GO(TX, TW, TO)                                                                                             \
-  launch_pdl(head_linear_kernel<TX, TW, TO>, grid, block, 0, stream, (const TX*)x, ldx, xhs, (const TW*)w, (TO*)out, \
-             ldo, ohs, M, N, K, token_req)
-  if (dtype == MLXB_F32) HL_GO(float, float, float);
+  if (few)                                                                                                            \
+    launch_pdl(head_linear_rows_kernel<TX, TW, TO>, rgrid, block, 0, stream, (const TX*)x, ldx, xhs, (const TW*)w,   \
+               (TO*)out, ldo, ohs, M, N, K, token_req);                                                               \
+  else                                                                                                                \
+    launch_pdl(head_linear_kernel<TX, TW, TO>, grid, block, 0, stream, (const TX*)x, ldx, xhs, (const TW*)w, (TO*)out, \
+               ldo, ohs, M, N, K, token_req)
+  if (dtype == MLXB_F32) { HL_GO(float, float, float); }
   else if (dtype != MLXB_BF16) return mlxb_fail(MLXB_BAD_DTYPE, "head_linear: dtype code %d", dtype);
-  else if (x_f32 && out_f32) HL_GO(float, __nv_bfloat16, float);
-  else if (x_f32) HL_GO(float, __nv_bfloat16, __nv_bfloat16);
-  else if (out_f32) HL_GO(__nv_bfloat16, __nv_bfloat16, float);
-  else HL_GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
+  else if (x_f32 && out_f32) { HL_GO(float, __nv_bfloat16, float); }
+  else if (x_f32) { HL_GO(float, __nv_bfloat16, __nv_bfloat16); }
+  else if (out_f32) { HL_GO(__nv_bfloat16, __nv_bfloat16, float); }
+  else { HL_GO(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16); }
 #undef HL_GO
   return mlxb_check_launch("head_linear");
 }

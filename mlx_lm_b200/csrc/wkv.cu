@@ -99,7 +99,7 @@ constexpr int WK_NPT = 16;     // rows of a state column a thread holds
 constexpr int WK_SEG = 20;     // floats between the staged runs of 16 rows (keeps 16-byte loads of neighbouring lanes apart)
 constexpr int WK_CHUNK = 16;   // tokens staged at a time
 
-template <typename T, int NS>
+template <typename T, int NS, bool VEC>
 __global__ void __launch_bounds__(256)
 wkv_scan_kernel(const T* rkv, int ld, int r_off, int k_off, int v_off, const float* d_raw, int ldd,
                 const float* __restrict__ u, float* state, const int* __restrict__ slots,
@@ -136,29 +136,77 @@ wkv_scan_kernel(const T* rkv, int ld, int r_off, int k_off, int v_off, const flo
   for (int c0 = 0; c0 < n; c0 += WK_CHUNK) {
     const int nc = min(WK_CHUNK, n - c0);
     __syncthreads();
-    for (int e = tid; e < nc * K; e += nthreads) {
-      const int tok = e / K, kk = e - tok * K;
-      const size_t row = (size_t)(t0 + c0 + tok);
-      const int at = tok * NP + (kk / WK_NPT) * WK_SEG + (kk % WK_NPT);
-      sr[at] = to_f(rkv[row * ld + r_off + h * K + kk]);
-      sk[at] = to_f(rkv[row * ld + k_off + h * K + kk]);
-      sw[at] = expf(-expf(d_raw[row * ldd + h * K + kk]));
-    }
-    for (int e = tid; e < nc * VB; e += nthreads) {
-      const int tok = e / VB, c = e - tok * VB;
-      sv[e] = vb * VB + c < V ? to_f(rkv[(size_t)(t0 + c0 + tok) * ld + v_off + h * V + vb * VB + c]) : 0.f;
-    }
-    __syncthreads();
-    for (int tok = warp; tok < nc; tok += nwarps) {
-      float b = 0.f;
-      for (int kk = lane; kk < K; kk += 32) {
-        const int at = tok * NP + (kk / WK_NPT) * WK_SEG + (kk % WK_NPT);
-        b = fmaf(sr[at] * uh[kk], sk[at], b);
+    if (VEC) {
+      // eight key channels of a token a thread: the loads of r, k and the decay's input go out together; the eight
+      // threads of a token (neighbouring lanes) add up its bonus term sum_k r u k
+      const int per_tok = K / 8;
+      for (int e = tid; e < WK_CHUNK * per_tok; e += nthreads) {
+        const int tok = e / per_tok, kk = (e - tok * per_tok) * 8;
+        float b = 0.f;
+        if (tok < nc) {
+          const size_t row = (size_t)(t0 + c0 + tok);
+          float rv[8], kv[8], dv[8], uv[8];
+          const T* rp = rkv + row * ld + r_off + h * K + kk;
+          const T* kp = rkv + row * ld + k_off + h * K + kk;
+          const float* dp = d_raw + row * ldd + h * K + kk;
+          if (sizeof(T) == 2) {
+            const uint4 r8 = *reinterpret_cast<const uint4*>(rp), k8 = *reinterpret_cast<const uint4*>(kp);
+            unpack8(r8, rv);
+            unpack8(k8, kv);
+          } else {
+            *reinterpret_cast<float4*>(rv) = *reinterpret_cast<const float4*>(rp);
+            *reinterpret_cast<float4*>(rv + 4) = *reinterpret_cast<const float4*>(rp + 4);
+            *reinterpret_cast<float4*>(kv) = *reinterpret_cast<const float4*>(kp);
+            *reinterpret_cast<float4*>(kv + 4) = *reinterpret_cast<const float4*>(kp + 4);
+          }
+          *reinterpret_cast<float4*>(dv) = *reinterpret_cast<const float4*>(dp);
+          *reinterpret_cast<float4*>(dv + 4) = *reinterpret_cast<const float4*>(dp + 4);
+          *reinterpret_cast<float4*>(uv) = *reinterpret_cast<const float4*>(uh + kk);
+          *reinterpret_cast<float4*>(uv + 4) = *reinterpret_cast<const float4*>(uh + kk + 4);
+          const int at = tok * NP + (kk / WK_NPT) * WK_SEG + (kk % WK_NPT);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            sr[at + i] = rv[i];
+            sk[at + i] = kv[i];
+            sw[at + i] = expf(-expf(dv[i]));
+            b = fmaf(rv[i] * uv[i], kv[i], b);
+          }
+        }
+        // (per_tok is a power of two up to 32 here, so a token's threads are an aligned group of lanes)
+        for (int off = per_tok >> 1; off > 0; off >>= 1) b += __shfl_xor_sync(0xffffffffu, b, off);
+        if (tok < nc && (e % per_tok) == 0) sb[tok] = b;
       }
-      b = warp_sum(b);
-      if (lane == 0) sb[tok] = b;
+      for (int e = tid; e < nc * VB; e += nthreads) {
+        const int tok = e / VB, c = e - tok * VB;
+        sv[e] = vb * VB + c < V ? to_f(rkv[(size_t)(t0 + c0 + tok) * ld + v_off + h * V + vb * VB + c]) : 0.f;
+      }
+      __syncthreads();
+    } else {
+      for (int e = tid; e < nc * K; e += nthreads) {
+        const int tok = e / K, kk = e - tok * K;
+        const size_t row = (size_t)(t0 + c0 + tok);
+        const int at = tok * NP + (kk / WK_NPT) * WK_SEG + (kk % WK_NPT);
+        sr[at] = to_f(rkv[row * ld + r_off + h * K + kk]);
+        sk[at] = to_f(rkv[row * ld + k_off + h * K + kk]);
+        sw[at] = expf(-expf(d_raw[row * ldd + h * K + kk]));
+      }
+      for (int e = tid; e < nc * VB; e += nthreads) {
+        const int tok = e / VB, c = e - tok * VB;
+        sv[e] = vb * VB + c < V ? to_f(rkv[(size_t)(t0 + c0 + tok) * ld + v_off + h * V + vb * VB + c]) : 0.f;
+      }
+      __syncthreads();
+      for (int tok = warp; tok < nc; tok += nwarps) {
+        float b = 0.f;
+        for (int kk = lane; kk < K; kk += 32) {
+          const int at = tok * NP + (kk / WK_NPT) * WK_SEG + (kk % WK_NPT);
+          b = fmaf(sr[at] * uh[kk], sk[at], b);
+        }
+        b = warp_sum(b);
+        if (lane == 0) sb[tok] = b;
+      }
+      __syncthreads();
     }
-    __syncthreads();
+#pragma unroll 4
     for (int tok = 0; tok < nc; ++tok) {
       const float* pr = sr + tok * NP + s * WK_SEG;
       const float* pk = sk + tok * NP + s * WK_SEG;
@@ -208,7 +256,10 @@ MLXB_EXPORT int mlxb_wkv_scan(int dtype, const void* rkv, int ld, int r_off, int
   // few (request, head) pairs: the columns of a pair over several blocks, never below two warps a block
   const long long pairs = (long long)H * n_requests;
   const int sms = mlxb_sm_count();
-  int threads = pairs >= sms ? 256 : (2 * pairs >= sms ? 128 : 64);
+  int threads = 2 * pairs >= sms ? 256 : 128;
+  // 16-byte staging: K a power of two from 16 to 256 (a token's K/8 staging threads are an aligned group of lanes)
+  const bool vec = K >= 16 && K <= 256 && (K & (K - 1)) == 0 && ld % 8 == 0 && r_off % 8 == 0 && k_off % 8 == 0 && ldd % 4 == 0 &&
+                   (((uintptr_t)rkv | (uintptr_t)d_raw | (uintptr_t)u) & 15) == 0;
   if (threads < 2 * NS) threads = 2 * NS;
   const int unit = NS >= 32 ? 1 : 32 / NS;                 // columns that make a whole warp
   int VB = threads / NS;
@@ -219,11 +270,16 @@ MLXB_EXPORT int mlxb_wkv_scan(int dtype, const void* rkv, int ld, int r_off, int
   const size_t smem = sizeof(float) * ((size_t)WK_CHUNK * (3 * NS * WK_SEG + VB + 1));
 #define WK_GO(T, N)                                                                                                  \
   if (smem > 48 * 1024) {                                                                                            \
-    cudaError_t e = cudaFuncSetAttribute(wkv_scan_kernel<T, N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    cudaError_t e = cudaFuncSetAttribute(wkv_scan_kernel<T, N, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(wkv_scan_kernel<T, N, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
     if (e != cudaSuccess) return mlxb_fail((int)e, "wkv_scan: %zu bytes of shared memory: %s", smem, cudaGetErrorString(e)); \
   }                                                                                                                  \
-  launch_pdl(wkv_scan_kernel<T, N>, grid, dim3(threads), smem, stream, (const T*)rkv, ld, r_off, k_off, v_off, d_raw, \
-             ldd, u, state, slots, token_req, req_first_token, o, ldo, H, K, V, VB)
+  if (vec)                                                                                                           \
+    launch_pdl(wkv_scan_kernel<T, N, true>, grid, dim3(threads), smem, stream, (const T*)rkv, ld, r_off, k_off, v_off, d_raw, \
+               ldd, u, state, slots, token_req, req_first_token, o, ldo, H, K, V, VB);                               \
+  else                                                                                                               \
+    launch_pdl(wkv_scan_kernel<T, N, false>, grid, dim3(threads), smem, stream, (const T*)rkv, ld, r_off, k_off, v_off, d_raw, \
+               ldd, u, state, slots, token_req, req_first_token, o, ldo, H, K, V, VB)
 #define WK_NS(T)                 \
   switch (NS) {                  \
     case 1: WK_GO(T, 1); break;  \

@@ -947,7 +947,7 @@ def attention_wide(q, q_head_stride: int, positions, token_req, block_table, k_p
 
 _WIDE_TC_ARGS = [c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
                  c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int,
-                 c_int, c_void_p, c_void_p]
+                 c_int, c_void_p, c_void_p, c_int, c_void_p]
 
 WIDE_TC = _os.environ.get("MLXB_WIDE_TC", "1") != "0"     # 0: the kernel on the CUDA cores for bfloat16 too
 
@@ -962,12 +962,22 @@ def attention_wide_tc_supported(k_pool, v_pool, n_heads: int, key_dim: int, valu
                   int(v_pool.data_ptr() == k_pool.data_ptr())))
 
 
+def attention_wide_scratch(n_rows: int, n_heads: int, value_dim: int, window: int, chunk: int, max_len: int) -> int:
+    """Floats of scratch memory with which ``attention_wide_tiles`` splits the keys of single rows over several
+    CTAs (0: rows that see few keys are not split)."""
+    f, _ = _fn("attention_wide_tc", "mlxb_attention_wide_tc_scratch", [c_int] * 6)
+    f.restype = ctypes.c_longlong
+    return int(f(n_rows, n_heads, value_dim, int(window or 0), int(chunk or 0), max_len))
+
+
 def attention_wide_tiles(q, q_head_stride: int, tiles, n_tiles: int, tile_queries: int, block_table, k_pool, v_pool, out,
                          out_head_stride: int, n_heads: int, key_dim: int, value_dim: int, scale: float, status, stream,
-                         window: int = 0, chunk: int = 0, talk=None, gate=None) -> None:
+                         window: int = 0, chunk: int = 0, talk=None, gate=None, scratch=None, max_len: int = 0) -> None:
     """``attention_wide`` on tensor cores for bfloat16 pools.  Instead of token rows it takes tiles, int32
     ``[n_tiles, 4]`` = (first token row, queries, block-table row, first position) of at most ``tile_queries``
-    consecutive tokens of one request each (tiles of 0 queries are skipped)."""
+    consecutive tokens of one request each (tiles of 0 queries are skipped).  With ``scratch`` (float32, at least
+    ``attention_wide_scratch`` floats for ``n_tiles`` rows and ``max_len`` positions) and tiles of one query, a row's
+    keys are split over CTAs that each take 128 positions, and a second kernel merges their partial results."""
     _need(q, torch.float32, "attention_wide_tiles q")
     _need(k_pool, torch.bfloat16, "attention_wide_tiles k_pool")
     _need(v_pool, torch.bfloat16, "attention_wide_tiles v_pool")
@@ -991,7 +1001,7 @@ def attention_wide_tiles(q, q_head_stride: int, tiles, n_tiles: int, tile_querie
           _rows(q, "attention_wide_tiles q"), q_head_stride, _p(tiles), n_tiles, tile_queries, _p(block_table),
           block_table.shape[1], n_pages, page, n_heads, Hkv, key_dim, value_dim, krs, v_pool.shape[3], int(window or 0),
           int(chunk or 0), float(scale), _p(talk), _p(k_pool), _p(v_pool), _p(gate), ldg, _p(out),
-          _rows(out, "attention_wide_tiles out"), out_head_stride, _p(status), stream)
+          _rows(out, "attention_wide_tiles out"), out_head_stride, _p(status), _p(scratch), int(max_len), stream)
 
 
 def attention_wide_step(ctx, q, q_head_stride: int, cache_k, cache_v, block_table, out, out_head_stride: int, n_heads: int,
@@ -1005,9 +1015,11 @@ def attention_wide_step(ctx, q, q_head_stride: int, cache_k, cache_v, block_tabl
                                  cache_k, cache_v, out, out_head_stride, n_heads, key_dim, value_dim, scale, ctx.status,
                                  ctx.stream, window=window, chunk=chunk, talk=talk, gate=gate)
         if ctx.n_single and ctx.single_tiles is not None:
+            need = attention_wide_scratch(ctx.n_single, n_heads, value_dim, window, chunk, ctx.max_len)
+            scratch = ctx.ws.flat("attn_wide_partial", need, torch.float32) if need else None
             attention_wide_tiles(q, q_head_stride, ctx.single_tiles, ctx.n_single, 1, block_table, cache_k, cache_v, out,
                                  out_head_stride, n_heads, key_dim, value_dim, scale, ctx.status, ctx.stream,
-                                 window=window, chunk=chunk, talk=talk, gate=gate)
+                                 window=window, chunk=chunk, talk=talk, gate=gate, scratch=scratch, max_len=ctx.max_len)
         return
     attention_wide(q, q_head_stride, ctx.positions, ctx.token_req, block_table, cache_k, cache_v, out, out_head_stride,
                    n_heads, key_dim, value_dim, scale, ctx.status, ctx.stream, window=window, chunk=chunk, talk=talk,

@@ -51,6 +51,18 @@ def check_tiles(ops, qd, qhs, table, kp, vp, H, dk, dv, scale, window, chunk, ta
     got = out.double().cpu().view(T, H, dv)
     assert float((got[rows] - want[rows]).abs().max()) < 6e-3
     assert bool((out[5] == 7.0).all()) and bool((out[2] == 7.0).all())
+    # the same rows with their keys split over several CTAs and merged
+    need = ops.attention_wide_scratch(len(rows) + 1, H, dv, window, chunk, 4096)
+    assert (need > 0) == (min(x for x in (window, chunk, 4096) if x) > 193)
+    if need:
+        scratch = torch.full((need,), float("nan"), device=DEV)
+        out2 = torch.full((T, H * dv), 7.0, device=DEV)
+        ops.attention_wide_tiles(qd, qhs, singles, len(rows) + 1, 1, table, kp, vp, out2, dv, H, dk, dv, scale, status,
+                                 ops.current_stream(), window=window, chunk=chunk, talk=talk, gate=gate, scratch=scratch,
+                                 max_len=4096)
+        assert int(status.item()) == 0
+        assert float((out2.double().cpu().view(T, H, dv)[rows] - want[rows]).abs().max()) < 6e-3
+        assert bool((out2[5] == 7.0).all()) and bool((out2[2] == 7.0).all())
 
 
 @pytest.mark.parametrize("act", ACT)
@@ -59,6 +71,7 @@ def check_tiles(ops, qd, qhs, table, kp, vp, H, dk, dv, scale, window, chunk, ta
     (3, 3, 48, 40, 0, 100, True, False),
     (6, 1, 16, 24, 0, 7, True, True),
     (8, 2, 64, 64, 50, 0, False, False),
+    (8, 4, 64, 64, 0, 0, True, True),          # every key visible: single rows split over several CTAs
     (2, 2, 20, 7, 33, 64, True, True),        # rows that are no multiple of 16 bytes, an odd value width
     (1, 1, 8, 8, 1, 0, True, True),
 ])
