@@ -49,7 +49,7 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.com
 // seg: columns one key head gives (talk: dk, G segments side by side; else Dk8 = the key's columns rounded up to 8,
 // one segment).  shared_v: values are columns 0 .. Dv-1 of the key tile.
 template <typename TO>
-__global__ void __launch_bounds__(TC_THREADS)
+__global__ void __launch_bounds__(TC_THREADS, 2)
 attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict__ tiles, int subs, int TQ, int HG,
                          const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                          int Dk, int Dv, int DkE, int seg, int n_seg, int krs, int vrs, int shared_v, int window,
@@ -86,23 +86,26 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
   v_pool = after_wait(v_pool);
   gate = after_wait(gate);
   // ---- queries: float32 -> hi + lo; with talk, the heads' queries mixed into the key heads' segments
-  for (int e = tid; e < TC_M * DkE; e += TC_THREADS) {
+  const int rows_used = nq * HG;                             // rows 0 .. rows_used - 1 carry a (token, head)
+  for (int e = tid; e < rows_used * DkE; e += TC_THREADS) {
     const int r = e / DkE, col = e - r * DkE;
     const int tq = r / HG, h = h0 + r % HG;
     float v = 0.f;
-    if (tq < nq) {
-      const float* qt = q + (size_t)(t0 + tq) * ldq;
-      if (talk) {
-        const int c = col / seg, d = col - c * seg;
-        if (c < n_seg)
-          for (int i = 0; i < rep; ++i) v = fmaf(talk[h * Hq + c * rep + i], qt[(size_t)(c * rep + i) * qhs + d], v);
-      } else if (col < Dk) {
-        v = qt[(size_t)h * qhs + col];
-      }
+    const float* qt = q + (size_t)(t0 + tq) * ldq;
+    if (talk) {
+      const int c = col / seg, d = col - c * seg;
+      if (c < n_seg)
+        for (int i = 0; i < rep; ++i) v = fmaf(talk[h * Hq + c * rep + i], qt[(size_t)(c * rep + i) * qhs + d], v);
+    } else if (col < Dk) {
+      v = qt[(size_t)h * qhs + col];
     }
     const __nv_bfloat16 hi = __float2bfloat16_rn(v);
     sQh[r * ldk + col] = hi;
     sQl[r * ldk + col] = __float2bfloat16_rn(v - __bfloat162float(hi));
+  }
+  for (int e = rows_used * (ldk / 8) + tid; e < TC_M * (ldk / 8); e += TC_THREADS) {      // the empty rows: zeros
+    reinterpret_cast<uint4*>(sQh)[e] = make_uint4(0u, 0u, 0u, 0u);
+    reinterpret_cast<uint4*>(sQl)[e] = make_uint4(0u, 0u, 0u, 0u);
   }
   // the rows' visible ranges
   const int my_row = tid >> 3, my_sub = tid & 7;             // softmax: eight threads a row

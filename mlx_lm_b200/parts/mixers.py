@@ -439,7 +439,7 @@ class LatentAttention(Mixer):
         o_lat = ctx.ws.get("latent_o", T, H * R, torch.float32)
         if ops.recording():
             pairs, keys = visible_pairs(ctx, self.window, self.chunk)
-            ops.label(self.name + ".attention", pairs * H * 2.0 * (self.lat + R),
+            ops.label(self.name + ".latent.attention", pairs * H * 2.0 * (self.lat + R),
                       x.element_size() * keys * self.row + 4.0 * T * H * (self.lat + R))
         ops.attention_wide_step(ctx, q_lat, self.lat, cache.k, cache.k, cache.block_table, o_lat, R, H, self.lat, R,
                                 self.scale, window=self.window or 0, chunk=self.chunk or 0)

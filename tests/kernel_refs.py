@@ -36,6 +36,8 @@ def linear(x, w, bias=None, activation=None, residual=None):
         y = gelu_new(y)
     elif activation == "relu":
         y = torch.relu(y)
+    elif activation == "tanh":
+        y = torch.tanh(y)
     elif activation not in (None, "none"):
         raise ValueError(activation)
     if residual is not None:

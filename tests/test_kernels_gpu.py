@@ -265,7 +265,7 @@ def test_every_activation_of_the_list_in_every_linear_kernel(ops, M, N, K):
     and the Python side reads: each name of the list runs in the generic (both dtypes), the few-rows and the
     tcgen05 kernel and gives what the plain statement gives; a code outside the list is refused."""
     from mlx_lm_b200.parts.linear import ACTIVATIONS
-    assert set(ops.ACTIVATION_CODES) == {"none", "gelu_new", "relu"} and ACTIVATIONS[None] == ops.EPI_NONE
+    assert set(ops.ACTIVATION_CODES) == {"none", "gelu_new", "relu", "tanh"} and ACTIVATIONS[None] == ops.EPI_NONE
     g = torch.Generator().manual_seed(M + N)
     x32 = torch.randn(M, K, generator=g).to(torch.bfloat16).float()
     w32 = (torch.randn(N, K, generator=g) / math.sqrt(K)).to(torch.bfloat16).float()
