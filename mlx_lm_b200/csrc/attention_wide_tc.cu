@@ -1,6 +1,6 @@
 // The attention of attention_wide.cu on tensor cores (mma.sync, bfloat16 pages, float32 accumulation).
 //
-// A CTA takes 32 rows: TQ consecutive tokens of one request times HG neighbouring heads that share a value head
+// A CTA takes 32 rows (64 for portions where the shared memory allows it: two halves that share the key tiles): TQ consecutive tokens of one request times HG neighbouring heads that share a value head
 // (TQ * HG = 32; a single-token entry: one token, HG heads, the other rows empty), and walks the keys in blocks of
 // 64 positions that start at multiples of 64, so the order of additions for a row depends on its position only.
 //
@@ -11,7 +11,8 @@
 // token's G key heads laid side by side; the mixed query is made in float32 when the CTA loads its queries.
 //
 // Per block of keys: the K tile (and the V tile, unless the values are the first Dv columns of the key rows) comes
-// into shared memory by 16-byte cp.async through the block table; warp w takes the scores of keys 8w .. 8w+7 for
+// into shared memory by 16-byte cp.async through the block table, the next block's while this block is computed
+// where two buffers fit; warp w takes the scores of keys 8w .. 8w+7 for
 // all 32 rows (S = Q K^T), masked and scaled into shared memory in float32; eight threads a row keep the running
 // maximum and sum and write the weights as bfloat16; warp w then takes every eighth 8-column tile of the values
 // (O = O * corr + P V) in registers.  Masks: causal, a window, runs of `chunk` positions counted from 0.
@@ -46,28 +47,30 @@ __device__ __forceinline__ void cp_async_wait_all() { asm volatile("cp.async.com
 
 // tiles: int32 [n_tiles, 4] = (first token row, queries, block-table row, first position); a CTA takes tokens
 // sub*TQ .. of tile blockIdx.x / subs.  DkE: columns of a (mixed) query and of a key tile row, a multiple of 16;
-// seg: columns one key head gives (talk: dk, G segments side by side; else Dk8 = the key's columns rounded up to 8,
-// one segment).  shared_v: values are columns 0 .. Dv-1 of the key tile.
-template <typename TO>
-__global__ void __launch_bounds__(TC_THREADS, 2)
+// seg: columns one key head gives (talk: dk, G segments side by side; else the key's columns rounded up to 8, one
+// segment).  shared_v: values are columns 0 .. Dv-1 of the key tile.  MP: the CTA takes 32 * MP rows with 8 * MP warps
+// (two halves that share the key tiles).  nbuf = 2: the next block's tiles are fetched while this block is computed.
+template <typename TO, int MP>
+__global__ void __launch_bounds__(TC_THREADS * MP, MP == 1 ? 2 : 1)
 attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict__ tiles, int subs, int TQ, int HG,
                          const int* __restrict__ block_table, int max_pages, int n_pages, int page, int Hq, int Hkv,
                          int Dk, int Dv, int DkE, int seg, int n_seg, int krs, int vrs, int shared_v, int window,
                          int chunk, float scale, const float* __restrict__ talk, const __nv_bfloat16* k_pool,
                          const __nv_bfloat16* v_pool, const __nv_bfloat16* gate, int ldg, TO* __restrict__ out, int ldo,
-                         int ohs, int* __restrict__ status, int bps, int n_rel, float* __restrict__ scratch) {
+                         int ohs, int* __restrict__ status, int bps, int n_rel, float* __restrict__ scratch, int nbuf) {
+  constexpr int M = TC_M * MP, THREADS = TC_THREADS * MP;
   extern __shared__ __align__(16) unsigned char tc_smem[];
   const int ldk = DkE + 8, ldv = shared_v ? ldk : Dv + 8;
-  long long* sRow = reinterpret_cast<long long*>(tc_smem);                  // [TC_N]
-  float* sS = reinterpret_cast<float*>(sRow + TC_N);                        // [TC_M][TC_N + TC_SPAD]
-  float* sCorr = sS + TC_M * (TC_N + TC_SPAD);                              // [TC_M]
-  float* sL = sCorr + TC_M;                                                 // [TC_M]
-  __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(sL + TC_M);          // [TC_M][TC_N + TC_PPAD]
-  __nv_bfloat16* sQh = sP + TC_M * (TC_N + TC_PPAD);                        // [TC_M][ldk]
-  __nv_bfloat16* sQl = sQh + TC_M * ldk;                                    // [TC_M][ldk]
-  __nv_bfloat16* sK = sQl + TC_M * ldk;                                     // [TC_N][ldk]
-  __nv_bfloat16* sV = shared_v ? sK : sK + TC_N * ldk;                      // [TC_N][ldv]
+  float* sS = reinterpret_cast<float*>(tc_smem);                            // [M][TC_N + TC_SPAD]
+  float* sCorr = sS + M * (TC_N + TC_SPAD);                                 // [M]
+  float* sL = sCorr + M;                                                    // [M]
+  __nv_bfloat16* sP = reinterpret_cast<__nv_bfloat16*>(sL + M);             // [M][TC_N + TC_PPAD]
+  __nv_bfloat16* sQh = sP + M * (TC_N + TC_PPAD);                           // [M][ldk]
+  __nv_bfloat16* sQl = sQh + M * ldk;                                       // [M][ldk]
+  __nv_bfloat16* sK0 = sQl + M * ldk;                                       // [nbuf][TC_N][ldk]
+  __nv_bfloat16* sV0 = shared_v ? sK0 : sK0 + nbuf * TC_N * ldk;            // [nbuf][TC_N][ldv]
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int mp = warp / TC_WARPS, w8 = warp % TC_WARPS;                     // which half of the rows, which warp of it
   const int tile = blockIdx.x / subs, sub = blockIdx.x - tile * subs;
   const int t_first = tiles[4 * tile], n_tile = tiles[4 * tile + 1], bt_row = tiles[4 * tile + 2];
   const int nq = min(TQ, n_tile - sub * TQ);
@@ -78,16 +81,64 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
   int lo_min = 0;                                            // first visible key of the first token: the smallest of the CTA
   if (window > 0 && pos0 - window + 1 > lo_min) lo_min = pos0 - window + 1;
   if (chunk > 0 && (pos0 / chunk) * chunk > lo_min) lo_min = (pos0 / chunk) * chunk;
-  if (bps > 0 && ((lo_min / TC_N) / bps + (int)blockIdx.z) * bps * TC_N > pos0 + nq - 1) return;   // a split without keys
+  int p_max = pos0 + nq - 1;
+  int j_first = (lo_min / TC_N) * TC_N;
+  if (bps > 0) {
+    // single rows with their keys split over the CTAs of grid.z: this one takes the blocks bps*za .. bps*za + bps - 1,
+    // counted from position 0, and leaves an unnormalised partial result for the merge kernel
+    const int za = (lo_min / TC_N) / bps + blockIdx.z;
+    if (za * bps * TC_N > p_max) return;                     // a split without keys
+    j_first = max(j_first, za * bps * TC_N);
+    p_max = min(p_max, (za + 1) * bps * TC_N - 1);
+  }
   pdl_wait();
   pdl_trigger();
   q = after_wait(q);
   k_pool = after_wait(k_pool);
   v_pool = after_wait(v_pool);
   gate = after_wait(gate);
+
+  // The tiles of the block of keys that starts at j0, into buffer `buf`: 16-byte pieces through the block table;
+  // zeros where a key lies outside lo_min .. p_max, where a column pads the tile, or where a page is missing.
+  auto load_tiles = [&](int j0, int buf) {
+    __nv_bfloat16* dK = sK0 + buf * TC_N * ldk;
+    const int per_key = DkE / 8;
+    for (int e = tid; e < TC_N * per_key; e += THREADS) {
+      const int jj = e / per_key, col = (e - jj * per_key) * 8, j = j0 + jj;
+      const int c = col / seg, d = col - c * seg;
+      const __nv_bfloat16* src = nullptr;
+      if (j >= lo_min && j <= p_max && c < n_seg) {
+        const int lp = j / page;
+        const int pg = lp < max_pages ? bt[lp] : -1;
+        if (pg >= n_pages) atomicOr(status, MLXB_ST_PAGE_RANGE);
+        else if (pg < 0) atomicOr(status, MLXB_ST_POSITION_RANGE);     // a key inside the range has no page
+        else src = k_pool + (((size_t)pg * Hkv + (talk ? c : cv)) * page + (j % page)) * krs + d;
+      }
+      if (src) cp_async16(dK + jj * ldk + col, src);
+      else *reinterpret_cast<uint4*>(dK + jj * ldk + col) = make_uint4(0u, 0u, 0u, 0u);
+    }
+    if (!shared_v) {
+      __nv_bfloat16* dV = sV0 + buf * TC_N * ldv;
+      const int per_v = Dv / 8;
+      for (int e = tid; e < TC_N * per_v; e += THREADS) {
+        const int jj = e / per_v, col = (e - jj * per_v) * 8, j = j0 + jj;
+        const __nv_bfloat16* src = nullptr;
+        if (j >= lo_min && j <= p_max) {
+          const int lp = j / page;
+          const int pg = lp < max_pages ? bt[lp] : -1;
+          if (pg >= 0 && pg < n_pages) src = v_pool + (((size_t)pg * Hkv + cv) * page + (j % page)) * vrs + col;
+        }
+        if (src) cp_async16(dV + jj * ldv + col, src);
+        else *reinterpret_cast<uint4*>(dV + jj * ldv + col) = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+    asm volatile("cp.async.commit_group;" ::: "memory");
+  };
+  load_tiles(j_first, 0);
+
   // ---- queries: float32 -> hi + lo; with talk, the heads' queries mixed into the key heads' segments
   const int rows_used = nq * HG;                             // rows 0 .. rows_used - 1 carry a (token, head)
-  for (int e = tid; e < rows_used * DkE; e += TC_THREADS) {
+  for (int e = tid; e < rows_used * DkE; e += THREADS) {
     const int r = e / DkE, col = e - r * DkE;
     const int tq = r / HG, h = h0 + r % HG;
     float v = 0.f;
@@ -103,25 +154,19 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
     sQh[r * ldk + col] = hi;
     sQl[r * ldk + col] = __float2bfloat16_rn(v - __bfloat162float(hi));
   }
-  for (int e = rows_used * (ldk / 8) + tid; e < TC_M * (ldk / 8); e += TC_THREADS) {      // the empty rows: zeros
+  for (int e = rows_used * (ldk / 8) + tid; e < M * (ldk / 8); e += THREADS) {      // the empty rows: zeros
     reinterpret_cast<uint4*>(sQh)[e] = make_uint4(0u, 0u, 0u, 0u);
     reinterpret_cast<uint4*>(sQl)[e] = make_uint4(0u, 0u, 0u, 0u);
   }
   // the rows' visible ranges
   const int my_row = tid >> 3, my_sub = tid & 7;             // softmax: eight threads a row
   const int my_tq = my_row / HG;
-  const int my_p = my_tq < nq ? pos0 + my_tq : -1;
+  const int my_p = my_tq < nq ? min(pos0 + my_tq, p_max) : -1;
   int my_lo = 0;
-  if (window > 0 && my_p - window + 1 > my_lo) my_lo = my_p - window + 1;
-  if (chunk > 0 && (my_p / chunk) * chunk > my_lo) my_lo = (my_p / chunk) * chunk;
-  int p_max = pos0 + nq - 1;
-  int j_first = (lo_min / TC_N) * TC_N;
-  if (bps > 0) {
-    // single rows with their keys split over the CTAs of grid.z: this one takes the blocks bps*za .. bps*za + bps - 1,
-    // counted from position 0, and leaves an unnormalised partial result for the merge kernel
-    const int za = (lo_min / TC_N) / bps + blockIdx.z;
-    j_first = max(j_first, za * bps * TC_N);
-    p_max = min(p_max, (za + 1) * bps * TC_N - 1);
+  {
+    const int p_own = pos0 + my_tq;
+    if (window > 0 && p_own - window + 1 > my_lo) my_lo = p_own - window + 1;
+    if (chunk > 0 && (p_own / chunk) * chunk > my_lo) my_lo = (p_own / chunk) * chunk;
   }
   float m_run = -INFINITY, l_run = 0.f;
   float o[TC_NT][2][4];
@@ -133,53 +178,22 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
       for (int x = 0; x < 4; ++x) o[i][m][x] = 0.f;
   const int n_vt = Dv / 8;                                   // 8-column tiles of the values
   const int g = lane >> 2, tq4 = lane & 3;
+  const int row0 = mp * TC_M;                                // this warp's rows: row0 .. row0 + 31
 
+  int buf = 0;
   for (int j0 = j_first; j0 <= p_max; j0 += TC_N) {
-    __syncthreads();                                         // the block before is done with the tiles
-    if (tid < TC_N) {
-      const int j = j0 + tid;
-      long long row = -1;
-      if (j >= lo_min && j <= p_max) {
-        const int lp = j / page;
-        const int pg = lp < max_pages ? bt[lp] : -1;
-        if (pg >= n_pages) atomicOr(status, MLXB_ST_PAGE_RANGE);
-        else if (pg < 0) atomicOr(status, MLXB_ST_POSITION_RANGE);
-        else row = (long long)pg * Hkv * page + (j % page);
-      }
-      sRow[tid] = row;
-    }
-    __syncthreads();
-    {
-      const int per_key = DkE / 8;                           // 16-byte pieces of a key tile row
-      for (int e = tid; e < TC_N * per_key; e += TC_THREADS) {
-        const int jj = e / per_key, col = (e - jj * per_key) * 8;
-        const long long row = sRow[jj];
-        __nv_bfloat16* dst = sK + jj * ldk + col;
-        const int c = col / seg, d = col - c * seg;
-        if (row >= 0 && c < n_seg && d < seg)
-          cp_async16(dst, k_pool + (size_t)(row + (long long)(talk ? c : cv) * page) * krs + d);
-        else
-          *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
-      }
-      if (!shared_v) {
-        const int per_v = Dv / 8;
-        for (int e = tid; e < TC_N * per_v; e += TC_THREADS) {
-          const int jj = e / per_v, col = (e - jj * per_v) * 8;
-          const long long row = sRow[jj];
-          __nv_bfloat16* dst = sV + jj * ldv + col;
-          if (row >= 0) cp_async16(dst, v_pool + (size_t)(row + (long long)cv * page) * vrs + col);
-          else *reinterpret_cast<uint4*>(dst) = make_uint4(0u, 0u, 0u, 0u);
-        }
-      }
-      cp_async_wait_all();
-    }
-    __syncthreads();
-    // ---- S = Q K^T for keys 8 warp .. 8 warp + 7
+    asm volatile("cp.async.wait_group 0;" ::: "memory");
+    __syncthreads();                                         // this block's tiles have landed; the block before is done with
+    const bool more = j0 + TC_N <= p_max;
+    if (nbuf == 2 && more) load_tiles(j0 + TC_N, buf ^ 1);
+    const __nv_bfloat16* sK = sK0 + buf * TC_N * ldk;
+    const __nv_bfloat16* sV = sV0 + buf * TC_N * ldv;
+    // ---- S = Q K^T for keys 8 w8 .. 8 w8 + 7 and this half's rows
     {
       float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
-      const unsigned kb = smem_addr(sK + (warp * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8);
-      const unsigned qh = smem_addr(sQh + (lane & 15) * ldk + (lane >> 4) * 8);
-      const unsigned ql = smem_addr(sQl + (lane & 15) * ldk + (lane >> 4) * 8);
+      const unsigned kb = smem_addr(sK + (w8 * 8 + (lane & 7)) * ldk + ((lane >> 3) & 1) * 8);
+      const unsigned qh = smem_addr(sQh + (row0 + (lane & 15)) * ldk + (lane >> 4) * 8);
+      const unsigned ql = smem_addr(sQl + (row0 + (lane & 15)) * ldk + (lane >> 4) * 8);
       for (int k0 = 0; k0 < DkE; k0 += 16) {
         unsigned b[2], a[4];
         ldmatrix_x2(b, kb + k0 * 2);
@@ -195,7 +209,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
       for (int m = 0; m < 2; ++m)
 #pragma unroll
         for (int x = 0; x < 4; ++x) {
-          const int r = m * 16 + g + (x >> 1) * 8, jj = warp * 8 + tq4 * 2 + (x & 1);
+          const int r = row0 + m * 16 + g + (x >> 1) * 8, jj = w8 * 8 + tq4 * 2 + (x & 1);
           sS[r * (TC_N + TC_SPAD) + jj] = s[m][x] * scale;
         }
     }
@@ -207,8 +221,7 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
         const int jj = my_sub * 8 + i, j = j0 + jj;
-        const bool vis = j <= my_p && j >= my_lo && sRow[jj] >= 0;
-        sv[i] = vis ? sS[my_row * (TC_N + TC_SPAD) + jj] : -INFINITY;
+        sv[i] = (j <= my_p && j >= my_lo) ? sS[my_row * (TC_N + TC_SPAD) + jj] : -INFINITY;
         mb = fmaxf(mb, sv[i]);
       }
       mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
@@ -237,16 +250,16 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
     {
       float cr[2][2];
 #pragma unroll
-      for (int m = 0; m < 2; ++m) { cr[m][0] = sCorr[m * 16 + g]; cr[m][1] = sCorr[m * 16 + g + 8]; }
+      for (int m = 0; m < 2; ++m) { cr[m][0] = sCorr[row0 + m * 16 + g]; cr[m][1] = sCorr[row0 + m * 16 + g + 8]; }
       unsigned a[2][4][4];                                   // P: two row tiles x four key steps
-      const unsigned pb = smem_addr(sP + (lane & 15) * (TC_N + TC_PPAD) + (lane >> 4) * 8);
+      const unsigned pb = smem_addr(sP + (row0 + (lane & 15)) * (TC_N + TC_PPAD) + (lane >> 4) * 8);
 #pragma unroll
       for (int m = 0; m < 2; ++m)
 #pragma unroll
         for (int ks = 0; ks < 4; ++ks) ldmatrix_x4(a[m][ks], pb + (m * 16 * (TC_N + TC_PPAD) + ks * 16) * 2);
 #pragma unroll
       for (int i = 0; i < TC_NT; ++i) {
-        const int nt = warp + i * TC_WARPS;
+        const int nt = w8 + i * TC_WARPS;
         if (nt < n_vt) {
 #pragma unroll
           for (int m = 0; m < 2; ++m) {
@@ -264,11 +277,17 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
         }
       }
     }
+    if (nbuf == 2) {
+      buf ^= 1;
+    } else if (more) {
+      __syncthreads();                                       // one buffer: everybody is done with it before it is refilled
+      load_tiles(j0 + TC_N, 0);
+    }
   }
   if (my_sub == 0) sL[my_row] = l_run;
   __syncthreads();
   if (bps > 0) {
-    // partial results (TQ = 1: row r is head h0 + r): [tile, head, split][Dv values | maximum | sum]
+    // partial results (one token: row r is head h0 + r): [tile, head, split][Dv values | maximum | sum]
     const size_t stride = (size_t)Dv + 2;
     if (my_sub == 0 && my_row < HG) {
       float* sp = scratch + (((size_t)tile * Hq + h0 + my_row) * n_rel + blockIdx.z) * stride;
@@ -277,13 +296,13 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
     }
 #pragma unroll
     for (int i = 0; i < TC_NT; ++i) {
-      const int nt = warp + i * TC_WARPS;
+      const int nt = w8 + i * TC_WARPS;
       if (nt >= n_vt) continue;
 #pragma unroll
       for (int m = 0; m < 2; ++m)
 #pragma unroll
         for (int half = 0; half < 2; ++half) {
-          const int r = m * 16 + g + half * 8;
+          const int r = row0 + m * 16 + g + half * 8;
           if (r >= HG) continue;
           float* sp = scratch + (((size_t)tile * Hq + h0 + r) * n_rel + blockIdx.z) * stride + nt * 8 + tq4 * 2;
           sp[0] = o[i][m][half * 2];
@@ -294,13 +313,13 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
   }
 #pragma unroll
   for (int i = 0; i < TC_NT; ++i) {
-    const int nt = warp + i * TC_WARPS;
+    const int nt = w8 + i * TC_WARPS;
     if (nt >= n_vt) continue;
 #pragma unroll
     for (int m = 0; m < 2; ++m)
 #pragma unroll
       for (int half = 0; half < 2; ++half) {
-        const int r = m * 16 + g + half * 8;
+        const int r = row0 + m * 16 + g + half * 8;
         const int tq = r / HG, h = h0 + r % HG;
         if (tq >= nq) continue;
         const float l = sL[r];
@@ -368,35 +387,51 @@ MLXB_EXPORT long long mlxb_attention_wide_tc_scratch(int n_rows, int Hq, int Dv,
   return (long long)n_rows * Hq * n_rel * (Dv + 2);
 }
 
-// What the launch needs of shared memory, or -1 if the sizes are not served (the caller then takes the kernel on the
-// CUDA cores): key and value widths in whole 16-byte pieces, at most 512 value columns, heads that group.
-static long long tc_plan(int Hq, int Hkv, int Dk, int Dv, int krs, int vrs, int talk, int shared_v, int* DkE, int* seg,
-                         int* n_seg, int* HG) {
-  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || Dv % 8 || Dv > 64 * TC_NT || krs % 8 || vrs % 8) return -1;
+// How a launch is laid out, or false if the sizes are not served (the caller then takes the kernel on the CUDA
+// cores): key and value widths in whole 16-byte pieces, at most 512 value columns, heads that group.  Portions take
+// 64 rows a CTA and two buffers for the key tiles where the shared memory allows it, else 32 rows, else one buffer.
+struct TcPlan { int DkE, seg, n_seg, HG, MP, nbuf; long long smem; };
+static bool tc_plan(int Hq, int Hkv, int Dk, int Dv, int krs, int vrs, int talk, int shared_v, bool portions, TcPlan* p) {
+  if (Hq <= 0 || Hkv <= 0 || Hq % Hkv || Dv % 8 || Dv > 64 * TC_NT || krs % 8 || vrs % 8) return false;
   const int rep = Hq / Hkv;
   if (talk) {
-    if (Dk % 8) return -1;
-    *seg = Dk;
-    *n_seg = Hkv;
+    if (Dk % 8) return false;
+    p->seg = Dk;
+    p->n_seg = Hkv;
   } else {
-    *seg = (Dk + 7) / 8 * 8;          // the pool's rows are zero beyond Dk
-    if (*seg > krs) return -1;
-    *n_seg = 1;
+    p->seg = (Dk + 7) / 8 * 8;          // the pool's rows are zero beyond Dk
+    if (p->seg > krs) return false;
+    p->n_seg = 1;
   }
-  *DkE = ((*seg) * (*n_seg) + 15) / 16 * 16;
-  if (shared_v && Dv > *DkE) return -1;
+  p->DkE = (p->seg * p->n_seg + 15) / 16 * 16;
+  if (shared_v && Dv > p->DkE) return false;
   int hg = 1;
   while (hg * 2 <= TC_M && rep % (hg * 2) == 0) hg *= 2;
-  *HG = hg;
-  const int ldk = *DkE + 8, ldv = shared_v ? ldk : Dv + 8;
-  const long long bytes = 8LL * TC_N + 4LL * (TC_M * (TC_N + TC_SPAD) + 2 * TC_M) + 2LL * TC_M * (TC_N + TC_PPAD) +
-                          2LL * (2 * TC_M + TC_N) * ldk + (shared_v ? 0LL : 2LL * TC_N * ldv);
-  return bytes <= 200 * 1024 ? bytes : -1;
+  p->HG = hg;
+  const int ldk = p->DkE + 8, ldv = shared_v ? ldk : Dv + 8;
+  auto bytes_of = [&](int MP, int nbuf) {
+    const int M = TC_M * MP;
+    return 4LL * (M * (TC_N + TC_SPAD) + 2 * M) + 2LL * M * (TC_N + TC_PPAD) + 2LL * 2 * M * ldk +
+           (long long)nbuf * (2LL * TC_N * ldk + (shared_v ? 0LL : 2LL * TC_N * ldv));
+  };
+  const long long whole = 220 * 1024, half = 110 * 1024;      // what one CTA, and what each of two CTAs of an SM, may take
+  // portions: 64 rows and two buffers; single rows: two CTAs an SM come before the second buffer
+  const int tries[5][3] = {{2, 2, 0}, {1, 2, 1}, {1, 1, 1}, {1, 2, 0}, {1, 1, 0}};
+  for (int i = portions ? 0 : 1; i < 5; ++i) {
+    const long long bytes = bytes_of(tries[i][0], tries[i][1]);
+    if (bytes <= (tries[i][2] ? half : whole)) {
+      p->MP = tries[i][0];
+      p->nbuf = tries[i][1];
+      p->smem = bytes;
+      return true;
+    }
+  }
+  return false;
 }
 
 MLXB_EXPORT int mlxb_attention_wide_tc_supported(int Hq, int Hkv, int Dk, int Dv, int krs, int vrs, int talk, int shared_v) {
-  int a, b, c, d;
-  return tc_plan(Hq, Hkv, Dk, Dv, krs, vrs, talk, shared_v, &a, &b, &c, &d) >= 0;
+  TcPlan p;
+  return tc_plan(Hq, Hkv, Dk, Dv, krs, vrs, talk, shared_v, false, &p) ? 1 : 0;
 }
 
 // The arguments of mlxb_attention_wide with bfloat16 pools, and instead of the token rows a list of tiles: int32
@@ -408,32 +443,35 @@ MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int
                                        int ldg, void* out, int ldo, int ohs, int* status, float* scratch, int max_len,
                                        cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  int DkE, seg, n_seg, HG;
+  TcPlan pl;
   const int shared_v = v_pool == k_pool;
-  const long long smem = tc_plan(Hq, Hkv, Dk, Dv, krs, vrs, talk != nullptr, shared_v, &DkE, &seg, &n_seg, &HG);
-  if (smem < 0 || page <= 0 || (page & (page - 1)) || tile_q <= 0 || qhs < Dk || ohs < Dv)
+  if (!tc_plan(Hq, Hkv, Dk, Dv, krs, vrs, talk != nullptr, shared_v, tile_q > 1, &pl) || page <= 0 || (page & (page - 1)) ||
+      tile_q <= 0 || qhs < Dk || ohs < Dv)
     return mlxb_fail(MLXB_BAD_ARG, "attention (wide, tensor cores): %d/%d heads, sizes %d/%d in rows of %d/%d", Hq, Hkv,
                      Dk, Dv, krs, vrs);
   // single rows with scratch memory: their keys split over grid.z, then merged
   const int n_rel = tc_splits(window, chunk, max_len);
-  const bool split = tile_q == 1 && scratch != nullptr && n_rel > 3;
-  const int TQ = split ? 1 : TC_M / HG;
+  // (only while the rows alone leave SMs idle: with more CTAs than SMs a split adds work and nothing else; a row's
+  // result is the same up to the rounding of the merge either way)
+  const bool split = tile_q == 1 && scratch != nullptr && n_rel > 3 && (long long)n_tiles * (Hq / pl.HG) < mlxb_sm_count();
+  const int TQ = split ? 1 : TC_M * pl.MP / pl.HG;
   const int subs = (tile_q + TQ - 1) / TQ;
   const int bps = split ? TC_BPS : 0;
-  const dim3 grid((unsigned)n_tiles * subs, Hq / HG, split ? n_rel : 1), block(TC_THREADS);
-#define TCW_GO(TO)                                                                                                     \
+  const long long smem = pl.smem;
+  const dim3 grid((unsigned)n_tiles * subs, Hq / pl.HG, split ? n_rel : 1), block(TC_THREADS * pl.MP);
+#define TCW_GO(TO, MPV)                                                                                                \
   do {                                                                                                                 \
-    auto kern = attention_wide_tc_kernel<TO>;                                                                          \
+    auto kern = attention_wide_tc_kernel<TO, MPV>;                                                                     \
     if (smem > 48 * 1024) {                                                                                            \
       cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);              \
       if (e != cudaSuccess)                                                                                            \
         return mlxb_fail((int)e, "attention (wide, tensor cores): %lld bytes of shared memory: %s", smem,              \
                          cudaGetErrorString(e));                                                                       \
     }                                                                                                                  \
-    launch_pdl(kern, grid, block, (size_t)smem, stream, q, ldq, qhs, tiles, subs, TQ, HG, block_table, max_pages,      \
-               n_pages, page, Hq, Hkv, Dk, Dv, DkE, seg, n_seg, krs, vrs, shared_v, window, chunk, scale, talk,        \
+    launch_pdl(kern, grid, block, (size_t)smem, stream, q, ldq, qhs, tiles, subs, TQ, pl.HG, block_table, max_pages,   \
+               n_pages, page, Hq, Hkv, Dk, Dv, pl.DkE, pl.seg, pl.n_seg, krs, vrs, shared_v, window, chunk, scale, talk, \
                (const __nv_bfloat16*)k_pool, (const __nv_bfloat16*)v_pool, (const __nv_bfloat16*)gate, ldg, (TO*)out,  \
-               ldo, ohs, status, bps, n_rel, scratch);                                                                 \
+               ldo, ohs, status, bps, n_rel, scratch, pl.nbuf);                                                        \
     if (split) {                                                                                                       \
       if (int e = mlxb_check_launch("attention (wide, tensor cores)")) return e;                                       \
       launch_pdl(attention_wide_merge_kernel<TO>, dim3(n_tiles, Hq), dim3(Dv >= 128 ? 128 : 64), 0, stream, tiles, Hq, \
@@ -441,8 +479,13 @@ MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int
                  ohs);                                                                                                 \
     }                                                                                                                  \
   } while (0)
-  if (out_f32) TCW_GO(float);
-  else TCW_GO(__nv_bfloat16);
+  if (pl.MP == 2) {
+    if (out_f32) TCW_GO(float, 2);
+    else TCW_GO(__nv_bfloat16, 2);
+  } else {
+    if (out_f32) TCW_GO(float, 1);
+    else TCW_GO(__nv_bfloat16, 1);
+  }
 #undef TCW_GO
   return mlxb_check_launch("attention (wide, tensor cores)");
 }
