@@ -195,14 +195,18 @@ attention_wide_tc_kernel(const float* q, int ldq, int qhs, const int* __restrict
       const unsigned qh = smem_addr(sQh + (row0 + (lane & 15)) * ldk + (lane >> 4) * 8);
       const unsigned ql = smem_addr(sQl + (row0 + (lane & 15)) * ldk + (lane >> 4) * 8);
       for (int k0 = 0; k0 < DkE; k0 += 16) {
-        unsigned b[2], a[4];
+        // the five fragment loads of a step go out together, then its four products
+        unsigned b[2], ah[2][4], al[2][4];
         ldmatrix_x2(b, kb + k0 * 2);
 #pragma unroll
         for (int m = 0; m < 2; ++m) {
-          ldmatrix_x4(a, qh + (m * 16 * ldk + k0) * 2);
-          mma_bf16(s[m], a, b);
-          ldmatrix_x4(a, ql + (m * 16 * ldk + k0) * 2);
-          mma_bf16(s[m], a, b);
+          ldmatrix_x4(ah[m], qh + (m * 16 * ldk + k0) * 2);
+          ldmatrix_x4(al[m], ql + (m * 16 * ldk + k0) * 2);
+        }
+#pragma unroll
+        for (int m = 0; m < 2; ++m) {
+          mma_bf16(s[m], ah[m], b);
+          mma_bf16(s[m], al[m], b);
         }
       }
 #pragma unroll

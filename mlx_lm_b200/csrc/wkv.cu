@@ -256,7 +256,7 @@ MLXB_EXPORT int mlxb_wkv_scan(int dtype, const void* rkv, int ld, int r_off, int
   // few (request, head) pairs: the columns of a pair over several blocks, never below two warps a block
   const long long pairs = (long long)H * n_requests;
   const int sms = mlxb_sm_count();
-  int threads = 2 * pairs >= sms ? 256 : 128;
+  int threads = 2 * pairs >= sms ? 256 : (4 * pairs >= sms ? 128 : 64);
   // 16-byte staging: K a power of two from 16 to 256 (a token's K/8 staging threads are an aligned group of lanes)
   const bool vec = K >= 16 && K <= 256 && (K & (K - 1)) == 0 && ld % 8 == 0 && r_off % 8 == 0 && k_off % 8 == 0 && ldd % 4 == 0 &&
                    (((uintptr_t)rkv | (uintptr_t)d_raw | (uintptr_t)u) & 15) == 0;

@@ -49,6 +49,10 @@ CONFIG_C = model(130, 80, [attention(dim=16, heads=6, kv_heads=1, vdim=24, rot_d
 CONFIG_W = model(128, 128, [attention(dim=64, heads=8, kv_heads=2, vdim=64, rot_dims=32, scale=0.125, chunk=128, mlp=DENSE(192)),
                             latent(dim=64, heads=4, kv_rank=256, rot_dim=64, vdim=64, scale=0.09, window=100),
                             wkv(dim=128, heads=2, decay_rank=32, mlp=DENSE(192))])
+# nothing is a multiple of 8: every 16-byte path steps aside (products, pages, staging, the tensor-core attention)
+CONFIG_ODD = model(77, 50, [attention(dim=12, heads=3, kv_heads=1, vdim=10, rot_dims=6, scale=0.3, chunk=9, mlp=DENSE(30)),
+                            latent(dim=6, heads=3, kv_rank=20, rot_dim=4, vdim=10, scale=0.3, window=11),
+                            wkv(dim=12, heads=3, decay_rank=3, mlp=DENSE(30))])
 ONLY_ATTENTION = model(64, 48, [attention(dim=16, heads=4, kv_heads=2, vdim=16, rot_dims=8, scale=0.25, chunk=40)])
 ONLY_LATENT = model(64, 48, [latent(dim=16, heads=3, kv_rank=16, rot_dim=8, vdim=16, scale=0.25, window=30)])
 ONLY_WKV = model(64, 48, [wkv(dim=16, heads=3, decay_rank=4)])

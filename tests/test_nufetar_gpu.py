@@ -12,13 +12,13 @@ import torch
 import plain_nufetar as plain
 from helpers import Trace, max_live_tokens, mixed_schedule, run_trace
 from lelatar_cases import run_engine, tokens, worst
-from nufetar_cases import (CONFIG_A, CONFIG_B, CONFIG_C, CONFIG_W, ONLY_ATTENTION, ONLY_LATENT, ONLY_WKV, make_dir,
+from nufetar_cases import (CONFIG_A, CONFIG_B, CONFIG_C, CONFIG_ODD, CONFIG_W, ONLY_ATTENTION, ONLY_LATENT, ONLY_WKV, make_dir,
                            sharpen, with_mask)
 
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "W": CONFIG_W, "attention": ONLY_ATTENTION,
+CONFIGS = {"A": CONFIG_A, "B": CONFIG_B, "C": CONFIG_C, "W": CONFIG_W, "odd": CONFIG_ODD, "attention": ONLY_ATTENTION,
            "latent": ONLY_LATENT, "wkv": ONLY_WKV}
 # Largest |difference| as a fraction of max(1, largest |logit| of the row).  float32: sums in another order.
 # bfloat16: the rounding of every product's inputs.  Measured on a B200: at most 1.0e-6 and 0.007 over all cases below; a key
@@ -240,3 +240,44 @@ def test_greedy_generation_through_the_entry_points(dtype, tmp_path):
     out = batch_generate(model, tokenizer, prompts, max_tokens=30, return_token_ids=True)
     for got, w, p in zip(out.token_ids, want, prompts):
         assert agrees(got, w, p), (got, w)
+
+
+def test_command_line_and_sampling(tmp_path):
+    """`python -m mlx_lm_b200 generate` on a model folder gives the Python entry point's tokens; the random-weights
+    mode builds the design from a config.json alone; samplers with filters run on its logits; and what is drawn
+    with a temperature does not depend on what else is in the batch."""
+    import json
+    import subprocess
+    import sys
+    from helpers import ROOT
+    from mlx_lm_b200 import generate, load
+    from mlx_lm_b200.generate import BatchGenerator
+    from mlx_lm_b200.sampling import make_sampler
+    config = CONFIG_C
+    make_dir(tmp_path / "m", config, seed=31, calmed=False, edit=lambda w: w.__setitem__("embed", w["embed"] * 0.25))
+    model, tokenizer = load(str(tmp_path / "m"), dtype="float32")
+    want = generate(model, tokenizer, [5, 17, 3], max_tokens=12)
+    run = lambda *a: subprocess.run([sys.executable, "-m", "mlx_lm_b200", "generate", *a], cwd=ROOT, capture_output=True,
+                                    text=True, timeout=300)
+    r = run("--model", str(tmp_path / "m"), "--prompt", "5 17 3", "-m", "12", "--dtype", "float32", "--verbose", "F")
+    assert r.returncode == 0, r.stderr
+    assert r.stdout.split() == want.split()
+    cfg = tmp_path / "config.json"
+    cfg.write_text(json.dumps(config))
+    r = run("--random-weights", "11", "--config", str(cfg), "--prompt", "5 17 3", "-m", "12", "--temp", "0.7",
+            "--top-p", "0.9", "--min-p", "0.01", "--top-k", "20", "--seed", "4", "--verbose", "F")
+    assert r.returncode == 0 and len(r.stdout.split()) == 12, r.stderr
+    prompts = [tokens(n, config["vocab"], n) for n in (5, 31, 64)]
+
+    def drawn(**kw):
+        gen = BatchGenerator(model, max_tokens=20, sampler=make_sampler(0.8, top_p=0.95), seed=1, **kw)
+        uids = gen.insert(prompts)
+        out = {u: [] for u in uids}
+        while gen.scheduler.has_work():
+            for resp in gen.next_generated():
+                out[resp.uid].append(resp.token)
+        return [out[u] for u in uids]
+    together = drawn(completion_batch_size=8, prefill_batch_size=8)
+    assert all(len(t) == 20 for t in together)
+    assert drawn(completion_batch_size=1, prefill_batch_size=1) == together
+    assert drawn(completion_batch_size=2, prefill_batch_size=1, prefill_step_size=7, max_tokens_per_step=9) == together
