@@ -197,7 +197,8 @@ MLXB_EXPORT int mlxb_head_linear(int dtype, int x_f32, int out_f32, const void* 
   if (M <= 0) return 0;
   if (N <= 0 || K <= 0 || H <= 0 || xhs < K || ohs < N || H > 65535)
     return mlxb_fail(MLXB_BAD_ARG, "head_linear: %d heads of %d x %d, head strides %d / %d", H, N, K, xhs, ohs);
-  const bool few = M <= 16;
+  // (float32 runs keep the tiled kernel whatever the step's size: a row's sum is then the same bits in every step)
+  const bool few = M <= 16 && dtype != MLXB_F32;
   const dim3 grid((N + HL_TN - 1) / HL_TN, (M + HL_TM - 1) / HL_TM, H), rgrid((N + 7) / 8, H, (M + 7) / 8), block(256);
 #define HL_GO(TX, TW, TO)                                                                                             \
   if (few)                                                                                                            \
