@@ -374,21 +374,25 @@ __global__ void attention_wide_merge_kernel(const int* __restrict__ tiles, int H
   }
 }
 
-constexpr int TC_BPS = 2;     // key blocks a CTA of a split single row takes: a constant, never a function of the batch
+constexpr int TC_BPS = 1;     // key blocks a CTA of a split single row takes: a constant, never a function of the batch
 
-// Splits a single row can have: the positions it can see, in blocks, over TC_BPS, and one more at either end.
-static int tc_splits(int window, int chunk, int max_len) {
+// Blocks of keys a single row can touch: the positions it can see, in blocks, and one more for a ragged start.
+static int tc_blocks(int window, int chunk, int max_len) {
   int span = max_len > 0 ? max_len : 1;
   if (window > 0 && window < span) span = window;
   if (chunk > 0 && chunk < span) span = chunk;
-  return ((span + TC_N - 1) / TC_N + 1) / TC_BPS + 2;
+  return (span + TC_N - 1) / TC_N + 1;
+}
+// Rows that see at most three blocks are not split; the others have room for this many partial results.
+static bool tc_splits_rows(int window, int chunk, int max_len) { return tc_blocks(window, chunk, max_len) > 3; }
+static int tc_splits(int window, int chunk, int max_len) {
+  return (tc_blocks(window, chunk, max_len) + TC_BPS - 1) / TC_BPS + 1;
 }
 
-// Floats of scratch memory that single rows need (0: rows that see at most two blocks are not split).
+// Floats of scratch memory that single rows need (0: rows that see few keys are not split).
 MLXB_EXPORT long long mlxb_attention_wide_tc_scratch(int n_rows, int Hq, int Dv, int window, int chunk, int max_len) {
-  const int n_rel = tc_splits(window, chunk, max_len);
-  if (n_rel <= 3) return 0;
-  return (long long)n_rows * Hq * n_rel * (Dv + 2);
+  if (!tc_splits_rows(window, chunk, max_len)) return 0;
+  return (long long)n_rows * Hq * tc_splits(window, chunk, max_len) * (Dv + 2);
 }
 
 // How a launch is laid out, or false if the sizes are not served (the caller then takes the kernel on the CUDA
@@ -457,7 +461,7 @@ MLXB_EXPORT int mlxb_attention_wide_tc(int out_f32, const float* q, int ldq, int
   const int n_rel = tc_splits(window, chunk, max_len);
   // (only while the rows alone leave SMs idle: with more CTAs than SMs a split adds work and nothing else; a row's
   // result is the same up to the rounding of the merge either way)
-  const bool split = tile_q == 1 && scratch != nullptr && n_rel > 3 && (long long)n_tiles * (Hq / pl.HG) < mlxb_sm_count();
+  const bool split = tile_q == 1 && scratch != nullptr && tc_splits_rows(window, chunk, max_len) && (long long)n_tiles * (Hq / pl.HG) < mlxb_sm_count();
   const int TQ = split ? 1 : TC_M * pl.MP / pl.HG;
   const int subs = (tile_q + TQ - 1) / TQ;
   const int bps = split ? TC_BPS : 0;

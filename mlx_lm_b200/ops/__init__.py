@@ -977,7 +977,7 @@ def attention_wide_tiles(q, q_head_stride: int, tiles, n_tiles: int, tile_querie
     ``[n_tiles, 4]`` = (first token row, queries, block-table row, first position) of at most ``tile_queries``
     consecutive tokens of one request each (tiles of 0 queries are skipped).  With ``scratch`` (float32, at least
     ``attention_wide_scratch`` floats for ``n_tiles`` rows and ``max_len`` positions) and tiles of one query, a row's
-    keys are split over CTAs that each take 128 positions, and a second kernel merges their partial results."""
+    keys are split over CTAs that each take 64 positions, and a second kernel merges their partial results."""
     _need(q, torch.float32, "attention_wide_tiles q")
     _need(k_pool, torch.bfloat16, "attention_wide_tiles k_pool")
     _need(v_pool, torch.bfloat16, "attention_wide_tiles v_pool")

@@ -53,7 +53,7 @@ def check_tiles(ops, qd, qhs, table, kp, vp, H, dk, dv, scale, window, chunk, ta
     assert bool((out[5] == 7.0).all()) and bool((out[2] == 7.0).all())
     # the same rows with their keys split over several CTAs and merged
     need = ops.attention_wide_scratch(len(rows) + 1, H, dv, window, chunk, 4096)
-    assert (need > 0) == (min(x for x in (window, chunk, 4096) if x) > 193)
+    assert (need > 0) == (min(x for x in (window, chunk, 4096) if x) > 128)
     if need:
         scratch = torch.full((need,), float("nan"), device=DEV)
         out2 = torch.full((T, H * dv), 7.0, device=DEV)
