@@ -104,7 +104,7 @@ __global__ void __launch_bounds__(256)
 wkv_scan_kernel(const T* rkv, int ld, int r_off, int k_off, int v_off, const float* d_raw, int ldd,
                 const float* __restrict__ u, float* state, const int* __restrict__ slots,
                 const int* __restrict__ token_req, const int* __restrict__ req_first_token, float* __restrict__ o,
-                int ldo, int H, int K, int V, int VB) {
+                int ldo, int H, int K, int V, int VB, bool pre) {
   extern __shared__ __align__(16) float wk_sm[];
   constexpr int NP = NS * WK_SEG;
   float* sr = wk_sm;                       // [CHUNK][NP]
@@ -133,6 +133,113 @@ wkv_scan_kernel(const T* rkv, int ld, int r_off, int k_off, int v_off, const flo
   }
   for (int e = tid; e < 3 * WK_CHUNK * NP; e += nthreads) sr[e] = 0.f;     // rows beyond K stay zero
   const float* uh = u + (size_t)h * K;
+  // the staged tokens of a chunk through the recurrence
+  auto run_tokens = [&](int c0, int nc) {
+#pragma unroll 4
+    for (int tok = 0; tok < nc; ++tok) {
+      const float* pr = sr + tok * NP + s * WK_SEG;
+      const float* pk = sk + tok * NP + s * WK_SEG;
+      const float* pw = sw + tok * NP + s * WK_SEG;
+      const float vv = sv[tok * VB + vl];
+      float a = 0.f;
+#pragma unroll
+      for (int i = 0; i < WK_NPT; i += 4) {
+        const float4 r4 = *reinterpret_cast<const float4*>(pr + i);
+        const float4 k4 = *reinterpret_cast<const float4*>(pk + i);
+        const float4 w4 = *reinterpret_cast<const float4*>(pw + i);
+        a = fmaf(r4.x, S[i], a);
+        a = fmaf(r4.y, S[i + 1], a);
+        a = fmaf(r4.z, S[i + 2], a);
+        a = fmaf(r4.w, S[i + 3], a);
+        S[i] = fmaf(w4.x, S[i], k4.x * vv);
+        S[i + 1] = fmaf(w4.y, S[i + 1], k4.y * vv);
+        S[i + 2] = fmaf(w4.z, S[i + 2], k4.z * vv);
+        S[i + 3] = fmaf(w4.w, S[i + 3], k4.w * vv);
+      }
+#pragma unroll
+      for (int off = NS / 2; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
+      if (s == 0 && valid) o[(size_t)(t0 + c0 + tok) * ldo + h * V + v] = fmaf(sb[tok], vv, a);
+    }
+  };
+  if (VEC && pre) {
+    // One staging item a thread (eight key channels of one token of the chunk) and the chunk after this one asked
+    // for before this one goes through the recurrence: the loads are in flight while the tokens are walked.
+    const int per_tok = K / 8;
+    const bool stager = tid < WK_CHUNK * per_tok;
+    const int tok_s = tid / per_tok, kk_s = (tid % per_tok) * 8;
+    float uv[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) uv[i] = stager ? uh[kk_s + i] : 0.f;
+    uint4 nr[2], nk[2];
+    float4 nd[2];
+    float nv[WK_CHUNK];
+    auto fetch = [&](int c0) {
+      const int nc = min(WK_CHUNK, n - c0);
+      if (stager && tok_s < nc) {
+        const size_t row = (size_t)(t0 + c0 + tok_s);
+        const T* rp = rkv + row * ld + r_off + h * K + kk_s;
+        const T* kp = rkv + row * ld + k_off + h * K + kk_s;
+        const float* dp = d_raw + row * ldd + h * K + kk_s;
+        nr[0] = *reinterpret_cast<const uint4*>(rp);
+        nk[0] = *reinterpret_cast<const uint4*>(kp);
+        if (sizeof(T) == 4) {
+          nr[1] = *reinterpret_cast<const uint4*>(rp + 4);
+          nk[1] = *reinterpret_cast<const uint4*>(kp + 4);
+        }
+        nd[0] = *reinterpret_cast<const float4*>(dp);
+        nd[1] = *reinterpret_cast<const float4*>(dp + 4);
+      }
+#pragma unroll
+      for (int i = 0; i < WK_CHUNK; ++i) {
+        const int e = tid + i * nthreads;
+        if (e < nc * VB) {
+          const int tok = e / VB, c = e - tok * VB;
+          nv[i] = vb * VB + c < V ? to_f(rkv[(size_t)(t0 + c0 + tok) * ld + v_off + h * V + vb * VB + c]) : 0.f;
+        }
+      }
+    };
+    fetch(0);
+    for (int c0 = 0; c0 < n; c0 += WK_CHUNK) {
+      const int nc = min(WK_CHUNK, n - c0);
+      __syncthreads();
+      if (stager) {
+        float b = 0.f;
+        if (tok_s < nc) {
+          float rv[8], kv[8], dv[8];
+          if (sizeof(T) == 2) {
+            unpack8(nr[0], rv);
+            unpack8(nk[0], kv);
+          } else {
+            *reinterpret_cast<uint4*>(rv) = nr[0];
+            *reinterpret_cast<uint4*>(rv + 4) = nr[1];
+            *reinterpret_cast<uint4*>(kv) = nk[0];
+            *reinterpret_cast<uint4*>(kv + 4) = nk[1];
+          }
+          *reinterpret_cast<float4*>(dv) = nd[0];
+          *reinterpret_cast<float4*>(dv + 4) = nd[1];
+          const int at = tok_s * NP + (kk_s / WK_NPT) * WK_SEG + (kk_s % WK_NPT);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            sr[at + i] = rv[i];
+            sk[at + i] = kv[i];
+            sw[at + i] = expf(-expf(dv[i]));
+            b = fmaf(rv[i] * uv[i], kv[i], b);
+          }
+        }
+        // (the stagers are whole warps, and a token's per_tok threads an aligned group of lanes)
+        for (int off = per_tok >> 1; off > 0; off >>= 1) b += __shfl_xor_sync(0xffffffffu, b, off);
+        if (tok_s < nc && kk_s == 0) sb[tok_s] = b;
+      }
+#pragma unroll
+      for (int i = 0; i < WK_CHUNK; ++i) {
+        const int e = tid + i * nthreads;
+        if (e < nc * VB) sv[e] = nv[i];
+      }
+      __syncthreads();
+      if (c0 + WK_CHUNK < n) fetch(c0 + WK_CHUNK);
+      run_tokens(c0, nc);
+    }
+  } else
   for (int c0 = 0; c0 < n; c0 += WK_CHUNK) {
     const int nc = min(WK_CHUNK, n - c0);
     __syncthreads();
@@ -206,31 +313,7 @@ wkv_scan_kernel(const T* rkv, int ld, int r_off, int k_off, int v_off, const flo
       }
       __syncthreads();
     }
-#pragma unroll 4
-    for (int tok = 0; tok < nc; ++tok) {
-      const float* pr = sr + tok * NP + s * WK_SEG;
-      const float* pk = sk + tok * NP + s * WK_SEG;
-      const float* pw = sw + tok * NP + s * WK_SEG;
-      const float vv = sv[tok * VB + vl];
-      float a = 0.f;
-#pragma unroll
-      for (int i = 0; i < WK_NPT; i += 4) {
-        const float4 r4 = *reinterpret_cast<const float4*>(pr + i);
-        const float4 k4 = *reinterpret_cast<const float4*>(pk + i);
-        const float4 w4 = *reinterpret_cast<const float4*>(pw + i);
-        a = fmaf(r4.x, S[i], a);
-        a = fmaf(r4.y, S[i + 1], a);
-        a = fmaf(r4.z, S[i + 2], a);
-        a = fmaf(r4.w, S[i + 3], a);
-        S[i] = fmaf(w4.x, S[i], k4.x * vv);
-        S[i + 1] = fmaf(w4.y, S[i + 1], k4.y * vv);
-        S[i + 2] = fmaf(w4.z, S[i + 2], k4.z * vv);
-        S[i + 3] = fmaf(w4.w, S[i + 3], k4.w * vv);
-      }
-#pragma unroll
-      for (int off = NS / 2; off > 0; off >>= 1) a += __shfl_xor_sync(0xffffffffu, a, off);
-      if (s == 0 && valid) o[(size_t)(t0 + c0 + tok) * ldo + h * V + v] = fmaf(sb[tok], vv, a);
-    }
+    run_tokens(c0, nc);
   }
   if (valid) {
 #pragma unroll
@@ -267,6 +350,7 @@ MLXB_EXPORT int mlxb_wkv_scan(int dtype, const void* rkv, int ld, int r_off, int
   if (VB > v_up) VB = v_up;
   threads = VB * NS;
   const dim3 grid(H, n_requests, (V + VB - 1) / VB);
+  const bool pre = vec && 2 * K <= threads;      // a staging item a thread: the next chunk is fetched ahead
   const size_t smem = sizeof(float) * ((size_t)WK_CHUNK * (3 * NS * WK_SEG + VB + 1));
 #define WK_GO(T, N)                                                                                                  \
   if (smem > 48 * 1024) {                                                                                            \
@@ -276,10 +360,10 @@ MLXB_EXPORT int mlxb_wkv_scan(int dtype, const void* rkv, int ld, int r_off, int
   }                                                                                                                  \
   if (vec)                                                                                                           \
     launch_pdl(wkv_scan_kernel<T, N, true>, grid, dim3(threads), smem, stream, (const T*)rkv, ld, r_off, k_off, v_off, d_raw, \
-               ldd, u, state, slots, token_req, req_first_token, o, ldo, H, K, V, VB);                               \
+               ldd, u, state, slots, token_req, req_first_token, o, ldo, H, K, V, VB, pre);                          \
   else                                                                                                               \
     launch_pdl(wkv_scan_kernel<T, N, false>, grid, dim3(threads), smem, stream, (const T*)rkv, ld, r_off, k_off, v_off, d_raw, \
-               ldd, u, state, slots, token_req, req_first_token, o, ldo, H, K, V, VB)
+               ldd, u, state, slots, token_req, req_first_token, o, ldo, H, K, V, VB, false)
 #define WK_NS(T)                 \
   switch (NS) {                  \
     case 1: WK_GO(T, 1); break;  \
