@@ -157,6 +157,122 @@ head_linear_kernel(const TX* x, int ldx, int xhs, const TW* __restrict__ w, TO* 
   }
 }
 
+// The same on tensor cores (mma.sync, bfloat16 weights) for steps of many rows: a tile of 64 tokens x 64 outputs of one
+// head a CTA, four warps with 16 tokens each, k in pieces of 64 through shared memory.  A float32 x is used as two
+// bfloat16 halves (hi + lo, two products per tile), so nothing of it is lost; sums are float32.
+__device__ __forceinline__ unsigned hl_smem(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void hl_ldmatrix_x4(unsigned (&r)[4], unsigned addr) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void hl_mma(float (&d)[4], const unsigned (&a)[4], unsigned b0, unsigned b1) {
+  asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+               : "+f"(d[0]), "+f"(d[1]), "+f"(d[2]), "+f"(d[3])
+               : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+
+constexpr int HT_KC = 64, HT_LD = HT_KC + 8;
+
+template <typename TX, typename TO, bool VEC>
+__global__ void __launch_bounds__(128)
+head_linear_tc_kernel(const TX* x, int ldx, int xhs, const __nv_bfloat16* __restrict__ w, TO* __restrict__ out, int ldo,
+                      int ohs, int M, int N, int K, const int* __restrict__ token_req) {
+  constexpr bool SPLIT = sizeof(TX) == 4;
+  __shared__ __align__(16) __nv_bfloat16 sxh[64 * HT_LD];
+  __shared__ __align__(16) __nv_bfloat16 sxl[SPLIT ? 64 * HT_LD : 8];
+  __shared__ __align__(16) __nv_bfloat16 sw[64 * HT_LD];
+  const int h = blockIdx.z, m0 = blockIdx.y * 64, n0 = blockIdx.x * 64;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  pdl_wait();
+  pdl_trigger();
+  x = after_wait(x);
+  const TX* xh = x + (size_t)h * xhs;
+  const __nv_bfloat16* wh = w + (size_t)h * N * K;
+  float acc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int e = 0; e < 4; ++e) acc[j][e] = 0.f;
+  for (int k0 = 0; k0 < K; k0 += HT_KC) {
+    __syncthreads();
+    if (VEC) {
+      // eight k of a row a thread, 16 bytes a load (two for a float32 x); K is a multiple of 8: a piece is all in or out
+      for (int e = tid; e < 64 * (HT_KC / 8); e += 128) {
+        const int rr = e / (HT_KC / 8), kk = (e - rr * (HT_KC / 8)) * 8;
+        const int m = m0 + rr, n = n0 + rr, k = k0 + kk;
+        uint4 wv = make_uint4(0u, 0u, 0u, 0u);
+        if (n < N && k < K) wv = *reinterpret_cast<const uint4*>(wh + (size_t)n * K + k);
+        *reinterpret_cast<uint4*>(sw + rr * HT_LD + kk) = wv;
+        if (SPLIT) {
+          float xv[8], hi[8], lo[8];
+#pragma unroll
+          for (int i = 0; i < 8; ++i) xv[i] = 0.f;
+          if (m < M && k < K) {
+            const float* xp = reinterpret_cast<const float*>(xh) + (size_t)m * ldx + k;
+            *reinterpret_cast<float4*>(xv) = *reinterpret_cast<const float4*>(xp);
+            *reinterpret_cast<float4*>(xv + 4) = *reinterpret_cast<const float4*>(xp + 4);
+          }
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            hi[i] = __bfloat162float(__float2bfloat16_rn(xv[i]));
+            lo[i] = xv[i] - hi[i];
+          }
+          *reinterpret_cast<uint4*>(sxh + rr * HT_LD + kk) = pack8(hi);
+          *reinterpret_cast<uint4*>(sxl + rr * HT_LD + kk) = pack8(lo);
+        } else {
+          uint4 xv = make_uint4(0u, 0u, 0u, 0u);
+          if (m < M && k < K) xv = *reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(xh) + (size_t)m * ldx + k);
+          *reinterpret_cast<uint4*>(sxh + rr * HT_LD + kk) = xv;
+        }
+      }
+    } else
+    for (int e = tid; e < 64 * HT_KC; e += 128) {
+      const int rr = e / HT_KC, kk = e - rr * HT_KC;
+      const int m = m0 + rr, n = n0 + rr, k = k0 + kk;
+      const float xv = (m < M && k < K) ? to_f(xh[(size_t)m * ldx + k]) : 0.f;
+      const __nv_bfloat16 hi = __float2bfloat16_rn(xv);
+      sxh[rr * HT_LD + kk] = hi;
+      if (SPLIT) sxl[rr * HT_LD + kk] = __float2bfloat16_rn(xv - __bfloat162float(hi));
+      sw[rr * HT_LD + kk] = (n < N && k < K) ? wh[(size_t)n * K + k] : __float2bfloat16_rn(0.f);
+    }
+    __syncthreads();
+    const unsigned ah = hl_smem(sxh + (warp * 16 + (lane & 15)) * HT_LD + (lane >> 4) * 8);
+    const unsigned al = hl_smem(sxl + (SPLIT ? (warp * 16 + (lane & 15)) * HT_LD + (lane >> 4) * 8 : 0));
+    // weights: a group of four 8 x 8 pieces is two output tiles by two halves of a k step
+    const unsigned wb = hl_smem(sw + ((lane & 7) + ((lane >> 4) & 1) * 8) * HT_LD + ((lane >> 3) & 1) * 8);
+#pragma unroll
+    for (int ks = 0; ks < HT_KC; ks += 16) {
+      unsigned a[4], a2[4];
+      hl_ldmatrix_x4(a, ah + ks * 2);
+      if (SPLIT) hl_ldmatrix_x4(a2, al + ks * 2);
+#pragma unroll
+      for (int jp = 0; jp < 4; ++jp) {
+        unsigned b[4];
+        hl_ldmatrix_x4(b, wb + (jp * 16 * HT_LD + ks) * 2);
+        hl_mma(acc[2 * jp], a, b[0], b[1]);
+        hl_mma(acc[2 * jp + 1], a, b[2], b[3]);
+        if (SPLIT) {
+          hl_mma(acc[2 * jp], a2, b[0], b[1]);
+          hl_mma(acc[2 * jp + 1], a2, b[2], b[3]);
+        }
+      }
+    }
+  }
+  const int g = lane >> 2, t4 = lane & 3;
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int m = m0 + warp * 16 + g + half * 8;
+    if (m >= M || (token_req && token_req[m] < 0)) continue;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int n = n0 + j * 8 + t4 * 2;
+      TO* op = out + (size_t)m * ldo + (size_t)h * ohs + n;
+      if (n < N) op[0] = from_f<TO>(acc[j][half * 2]);
+      if (n + 1 < N) op[1] = from_f<TO>(acc[j][half * 2 + 1]);
+    }
+  }
+}
+
 // The same for steps of few rows (single-token entries): a warp per output column and eight rows, the lanes side by
 // side along k (the weights are read once, in whole lines), partial sums added across the warp.
 template <typename TX, typename TW, typename TO>
@@ -200,6 +316,25 @@ MLXB_EXPORT int mlxb_head_linear(int dtype, int x_f32, int out_f32, const void* 
   // (float32 runs keep the tiled kernel whatever the step's size: a row's sum is then the same bits in every step)
   const bool few = M <= 16 && dtype != MLXB_F32;
   const dim3 grid((N + HL_TN - 1) / HL_TN, (M + HL_TM - 1) / HL_TM, H), rgrid((N + 7) / 8, H, (M + 7) / 8), block(256);
+  const bool tc = dtype == MLXB_BF16 && M > 16 && getenv("MLXB_HEAD_LINEAR_SIMT") == nullptr;
+  if (tc) {
+    const dim3 tgrid((N + 63) / 64, (M + 63) / 64, H), tblock(128);
+    const int xa = x_f32 ? 4 : 8;          // elements of x in 16 bytes
+    const bool vec = K % 8 == 0 && ldx % xa == 0 && xhs % xa == 0 && (((uintptr_t)x | (uintptr_t)w) & 15) == 0;
+#define HT_GO(TX, TO)                                                                                                 \
+  if (vec)                                                                                                            \
+    launch_pdl(head_linear_tc_kernel<TX, TO, true>, tgrid, tblock, 0, stream, (const TX*)x, ldx, xhs,                 \
+               (const __nv_bfloat16*)w, (TO*)out, ldo, ohs, M, N, K, token_req);                                      \
+  else                                                                                                                \
+    launch_pdl(head_linear_tc_kernel<TX, TO, false>, tgrid, tblock, 0, stream, (const TX*)x, ldx, xhs,                \
+               (const __nv_bfloat16*)w, (TO*)out, ldo, ohs, M, N, K, token_req)
+    if (x_f32 && out_f32) { HT_GO(float, float); }
+    else if (x_f32) { HT_GO(float, __nv_bfloat16); }
+    else if (out_f32) { HT_GO(__nv_bfloat16, float); }
+    else { HT_GO(__nv_bfloat16, __nv_bfloat16); }
+#undef HT_GO
+    return mlxb_check_launch("head_linear");
+  }
 #define HL_GO(TX, TW, TO)                                                                                             \
   if (few)                                                                                                            \
     launch_pdl(head_linear_rows_kernel<TX, TW, TO>, rgrid, block, 0, stream, (const TX*)x, ldx, xhs, (const TW*)w,   \

@@ -242,19 +242,20 @@ def test_a_product_per_head(H, N, K, T):
     torch.manual_seed(H * N + K)
     for wdt, xdt, odt in [(torch.float32, torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16, torch.float32),
                           (torch.bfloat16, torch.float32, torch.bfloat16), (torch.bfloat16, torch.float32, torch.float32)]:
-        xs, os_ = K + 3, N + 5                       # heads lie apart by more than their own width
-        x = torch.randn(T, H * xs).to(xdt)
-        w = (torch.randn(H, N, K) / math.sqrt(K)).to(wdt)
-        want = torch.einsum("thk,hnk->thn", x.double().view(T, H, xs)[..., :K], w.double())
-        out = torch.full((T, H * os_), 9.0, dtype=odt, device=DEV)
-        req = [0] * T
-        req[T // 2] = -1
-        ops.head_linear(x.to(DEV), xs, w.to(DEV), out, os_, ops.current_stream(), token_req=i32(req))
-        got = out.double().cpu().view(T, H, os_)
-        keep = [t for t in range(T) if t != T // 2]
-        tol = 2e-5 * math.sqrt(K) if odt == torch.float32 else 3e-2
-        assert float((got[keep][..., :N] - want[keep]).abs().max()) < tol, (wdt, xdt, odt)
-        assert bool((got[..., N:] == 9.0).all()) and bool((got[T // 2] == 9.0).all())
+      # heads lie apart by more than their own width; the second pair: strides that allow 16-byte loads
+      for xs, os_ in ((K + 3, N + 5), ((K + 7) // 8 * 8 + 8, N + 16)):
+          x = torch.randn(T, H * xs).to(xdt)
+          w = (torch.randn(H, N, K) / math.sqrt(K)).to(wdt)
+          want = torch.einsum("thk,hnk->thn", x.double().view(T, H, xs)[..., :K], w.double())
+          out = torch.full((T, H * os_), 9.0, dtype=odt, device=DEV)
+          req = [0] * T
+          req[T // 2] = -1
+          ops.head_linear(x.to(DEV), xs, w.to(DEV), out, os_, ops.current_stream(), token_req=i32(req))
+          got = out.double().cpu().view(T, H, os_)
+          keep = [t for t in range(T) if t != T // 2]
+          tol = 2e-5 * math.sqrt(K) if odt == torch.float32 else 3e-2
+          assert float((got[keep][..., :N] - want[keep]).abs().max()) < tol, (wdt, xdt, odt)
+          assert bool((got[..., N:] == 9.0).all()) and bool((got[T // 2] == 9.0).all())
 
 
 @pytest.mark.parametrize("act", ACT)
