@@ -27,7 +27,7 @@ MLXB_DEFINE_LAST_ERROR()
 constexpr int AW_THREADS = 256;
 constexpr int AW_KB = 64;      // keys per block
 constexpr int AW_MAXO = 8;     // (head, column group) items a thread accumulates
-constexpr int AW_MAXH = 32;    // heads a CTA takes at most
+constexpr int AW_MAXH = 64;    // heads a CTA takes at most
 
 template <typename T>
 struct KVec;   // 16 bytes of keys
